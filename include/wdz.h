@@ -1,0 +1,167 @@
+/*
+ * wdz.h - C ABI of the B200 transcription engine (libwdz.so).
+ *
+ * The reference project is pure Python and has no FFI of its own; its seam is
+ * the set of methods its Transcriber calls on the model object.  Each entry
+ * point below names the reference call it stands in for (paths inside the
+ * reference project).  Conventions:
+ *   - every function returns WDZ_OK (0) or a negative WDZ_E* code and never
+ *     throws or aborts; wdz_last_error() gives the text of the last failure;
+ *   - all buffers are caller-owned device memory (the Python host passes
+ *     torch ``data_ptr()`` values); "dev" in a comment means a device pointer,
+ *     "host" a host pointer; the engine allocates nothing on the device;
+ *   - calls are asynchronous on the given stream unless they fill host memory;
+ *   - an engine is not thread-safe; use one engine per GPU per process.
+ */
+#ifndef WDZ_H_
+#define WDZ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WDZ_OK 0
+#define WDZ_EINVAL (-1)    /* bad argument */
+#define WDZ_ENOMEM (-2)    /* workspace missing or too small */
+#define WDZ_ECUDA (-3)     /* a CUDA call failed */
+#define WDZ_ESTATE (-4)    /* engine not finalized, or a tensor was never bound */
+#define WDZ_ECAPACITY (-5) /* more clips / rows / slots than the engine was built for */
+#define WDZ_ENAN (-6)      /* a row of logits held NaN */
+#define WDZ_ETIMEOUT (-7)  /* a bounded device-side wait ran out */
+
+#define WDZ_F32 0
+#define WDZ_BF16 1
+
+typedef void* wdz_stream; /* a cudaStream_t */
+typedef struct wdz_engine wdz_engine;
+
+/* Shape of the model plus the capacities the workspace is sized for.  The
+ * first ten fields are the reference's ModelDimensions
+ * (src/whisperdrz/config.py:4-15). */
+typedef struct wdz_config {
+  int32_t n_mels, n_audio_ctx, n_audio_state, n_audio_head, n_audio_layer;
+  int32_t n_vocab, n_text_ctx, n_text_state, n_text_head, n_text_layer;
+  int32_t dtype;      /* WDZ_F32 or WDZ_BF16: type of weights, KV caches, encoder output */
+  int32_t n_slots;    /* KV slots (reference: BS + n_warm, transcriber.py:566-568) */
+  int32_t max_tokens; /* self-attention cache length per slot (transcriber.py:673-677) */
+  int32_t max_clips;  /* most 30 s windows per wdz_logmel / wdz_encode / wdz_cross_kv call */
+  int32_t max_rows;   /* most token rows per wdz_forward_rows / wdz_decode_step call */
+  int32_t flags;      /* WDZ_FLAG_* */
+} wdz_config;
+
+#define WDZ_FLAG_NO_TENSOR_CORE 1 /* keep bf16 GEMMs on the CUDA-core path (debug / A-B runs) */
+
+/* Per-row logit rule: the device half of decode_batch
+ * (src/whisperdrz/decoding.py:1514-1777).  Blocked set of a row =
+ *   base(mode) | OR of tables whose bit is set in table_bits
+ *   | ids in [prefix_begin, prefix_end) | set_ids[0..n_set)
+ * with clear_ids[0..n_clear) removed last.  Blocked ids get -65504 added
+ * (decoding.py:1725-1729); ids in pen_ids get the repetition penalty
+ * v > 0 ? v / 1.2 : v * 1.2 (decoding.py:1733-1759); then argmax, lowest id
+ * winning ties.  forced_id >= 0 skips all of that and returns forced_id
+ * (rows decided on the host, decoding.py:1098-1456). */
+#define WDZ_MODE_OR 0               /* base = nothing blocked */
+#define WDZ_MODE_ALL_EXCEPT_TABLE 1 /* base = everything blocked except table arg0 */
+#define WDZ_MODE_ALL_EXCEPT_RANGE 2 /* base = everything blocked except ids [arg0, arg1) */
+#define WDZ_MODE_ALL 3              /* base = everything blocked (use clear_ids) */
+#define WDZ_MAX_TABLES 32
+typedef struct wdz_rule_desc {
+  int32_t forced_id;
+  int32_t mode, arg0, arg1;
+  uint32_t table_bits;
+  int32_t prefix_begin, prefix_end;
+  int32_t n_set, set_ids[8];
+  int32_t n_clear, clear_ids[4];
+  int32_t n_pen, pen_ids[10];
+} wdz_rule_desc; /* 32 x int32 = 128 bytes */
+
+/* ---- life cycle ------------------------------------------------------- */
+/* Stands in for WhisperDRZ.__init__ + Transcriber.load_model
+ * (model.py:649-693, transcriber.py:642-726). */
+int wdz_engine_create(const wdz_config* cfg, wdz_engine** out);
+int wdz_engine_destroy(wdz_engine* e);
+/* Scratch the engine needs for the capacities in its config. */
+int wdz_workspace_bytes(const wdz_engine* e, size_t* out_bytes);
+int wdz_set_workspace(wdz_engine* e, void* dev, size_t bytes);
+/* Lend the engine one tensor (dtype = cfg.dtype unless noted).  Names are
+ * listed in whisperdrz_b200/engine.py (ENGINE_TENSORS): the reference's
+ * state_dict tensors (model.py:258-261,387-394,449-461,493-529), with q/k/v
+ * stacked per attention and the conv kernels tap-major, plus
+ *   cache.self_k / cache.self_v   [n_text_layer, n_slots, max_tokens, n_text_state]
+ *   cache.cross_k / cache.cross_v [n_text_layer, n_slots, n_audio_ctx, n_text_state]
+ *   cache.seq_lens                int32 [n_slots]
+ * (FlashKVCache, model.py:98-147, one allocation per kind instead of one
+ * object per layer) and rules.tables uint32 [WDZ_MAX_TABLES, ceil(n_vocab/32)]
+ * (the [V] bool class masks of DecoderState, decoding.py:397-724, as bitsets). */
+int wdz_bind(wdz_engine* e, const char* name, const void* dev, int64_t numel);
+int wdz_finalize(wdz_engine* e);
+const char* wdz_last_error(const wdz_engine* e);
+const char* wdz_version(void);
+/* Reads and clears the device-side error word (WDZ_OK, WDZ_ENAN, WDZ_ETIMEOUT).
+ * Synchronises the stream. */
+int wdz_device_status(wdz_engine* e, wdz_stream s);
+
+/* ---- front end: LogMelSpectrogram.forward (audio.py:108-156) ----------- */
+/* audio_dev f32 [B, audio_stride]; n_samples_dev int32 [B] (>= 400 each, the
+ * reflect padding needs it); frame_offset_dev int32 [B] or NULL: first frame
+ * of the 3000-frame window (continuation windows, transcriber.py:1062-1072).
+ * mel_out_dev f32 [B, n_mels, 3000]; frames past the clip are -1.5. */
+int wdz_logmel(wdz_engine* e, const float* audio_dev, int64_t audio_stride,
+               const int32_t* n_samples_dev, const int32_t* frame_offset_dev, int B,
+               float* mel_out_dev, wdz_stream s);
+
+/* ---- encoder: AudioEncoder.forward (model.py:462-475) ------------------ */
+/* mel_dev f32 [B, n_mels, 3000] -> xa_out_dev [B, n_audio_ctx, n_audio_state] in cfg.dtype */
+int wdz_encode(wdz_engine* e, const float* mel_dev, int B, void* xa_out_dev, wdz_stream s);
+
+/* ---- decoder ----------------------------------------------------------- */
+/* Cross K/V of all layers for B windows into their slots
+ * (WhisperDRZ.prefill_flash, model.py:852-855). slot_ids_dev int32 [B]. */
+int wdz_cross_kv(wdz_engine* e, const void* xa_dev, const int32_t* slot_ids_dev, int B,
+                 wdz_stream s);
+/* seq_lens[slot] = 0 (reset_flash_kv, model.py:813-822; prefill_flash :858-862). */
+int wdz_slot_reset(wdz_engine* e, const int32_t* slot_ids_dev, int n, wdz_stream s);
+/* Copies cache.seq_lens to host (FlashKVCache.seq_lens, read at transcriber.py:1676). Synchronises. */
+int wdz_slot_seqlens(wdz_engine* e, int32_t* out_host, wdz_stream s);
+
+/* TextDecoder.forward_flash (model.py:570-617) over ragged rows: row i feeds
+ * token tokens_dev[i] at position positions_dev[i] of slot slot_ids_dev[i];
+ * its K/V are appended there and it attends causally to [0, position] of that
+ * slot and to all encoder positions.  Rows of one slot must carry distinct
+ * positions (a prompt is P rows with positions 0..P-1).  Afterwards
+ * seq_lens[slot] = max(seq_lens[slot], position + 1).  Logits (f32 [n_emit,
+ * n_vocab]) are produced for rows emit_rows_dev[0..n_emit) only (NULL = all n
+ * rows); logits_out_dev may be NULL to keep them only inside the engine. */
+int wdz_forward_rows(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slot_ids_dev,
+                     const int32_t* positions_dev, int n, const int32_t* emit_rows_dev, int n_emit,
+                     float* logits_out_dev, wdz_stream s);
+/* prefill_flash (model.py:824-869): cross K/V + slot reset for the B windows,
+ * then wdz_forward_rows over the flattened prompt rows. */
+int wdz_prefill(wdz_engine* e, const void* xa_dev, const int32_t* window_slot_ids_dev, int B,
+                const int32_t* tokens_dev, const int32_t* slot_ids_dev, const int32_t* positions_dev,
+                int n, const int32_t* emit_rows_dev, int n_emit, float* logits_out_dev, wdz_stream s);
+/* One decode step for n_active rows (the loop body of transcriber.py:1666-1702):
+ * positions are read from cache.seq_lens on the device, logits stay resident
+ * in the engine, rules (NULL = plain argmax) are applied and the chosen ids
+ * written to next_tokens_out_dev int32 [n_active] (-1 for a NaN row).
+ * logits_out_dev: optional f32 [n_active, n_vocab] copy. */
+int wdz_decode_step(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slot_ids_dev, int n_active,
+                    const wdz_rule_desc* rules_dev, int32_t* next_tokens_out_dev,
+                    float* logits_out_dev, wdz_stream s);
+/* Phase-4 re-argmax (decoding.py:2033-2044, _sample_masked :2049-2067) on the
+ * logits of the last wdz_decode_step / wdz_forward_rows: rows_dev[i] indexes
+ * that call's logit rows; no repetition penalty. */
+int wdz_reargmax(wdz_engine* e, const int32_t* rows_dev, const wdz_rule_desc* rules_dev, int n,
+                 int32_t* out_dev, wdz_stream s);
+/* Phase 3 on caller-held logits f32 [n, n_vocab] (e.g. the first token after
+ * a prefill, transcriber.py:1109-1126). */
+int wdz_rules_argmax(wdz_engine* e, const float* logits_dev, const wdz_rule_desc* rules_dev, int n,
+                     int apply_penalty, int32_t* out_dev, wdz_stream s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WDZ_H_ */

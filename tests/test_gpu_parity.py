@@ -1,0 +1,242 @@
+"""GPU parity: the CUDA engine, called through the C ABI, against the CPU
+oracle and the golden vectors recorded from the reference.
+
+Tolerances: fp32 engine - greedy token ids identical, logits within 1e-3 of
+logit RMS, encoder states within 1e-4 relative L2; bf16 engine - teacher-forced
+logits within 3e-2 x logit RMS (max-abs), encoder states within 1e-2 relative
+L2; log-mel within 1e-3 max-abs; rule/argmax results identical.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from whisperdrz_b200 import synth
+from whisperdrz_b200.dims import ModelDimensions, TOK_EOT
+from whisperdrz_b200.weights import init_state_dict
+
+pytestmark = pytest.mark.gpu
+
+F32_LOGIT_TOL = 1e-3
+BF16_LOGIT_TOL = 3e-2
+F32_ENC_TOL = 1e-4
+BF16_ENC_TOL = 1e-2
+MEL_TOL = 1e-3
+
+
+def _engine(name, dtype, seed=0, **kw):
+    from whisperdrz_b200.engine import Engine
+    dims = ModelDimensions.from_name(name)
+    sd = init_state_dict(dims, seed)
+    return Engine(dims, sd, dtype=dtype, **kw), dims, sd
+
+
+@pytest.fixture(scope="module")
+def small_f32():
+    e, dims, sd = _engine("test-small", torch.float32, n_slots=6, max_clips=2)
+    yield e, dims, sd
+    e.close()
+
+
+@pytest.fixture(scope="module")
+def small_bf16():
+    e, dims, sd = _engine("test-small", torch.bfloat16, n_slots=6, max_clips=2)
+    yield e, dims, sd
+    e.close()
+
+
+def _oracle_mel(audio_np):
+    return torch.stack([oracle.window_mel(oracle.log_mel(torch.from_numpy(a))) for a in audio_np])
+
+
+# --------------------------------------------------------------------------- mel
+def test_logmel_matches_oracle_and_golden(small_f32, golden_dir):
+    e, _, _ = small_f32
+    g = np.load(os.path.join(golden_dir, "mel.npz"))
+    for name in ("clip30", "clip7", "clip1"):
+        a = synth.clip(int(g[f"{name}_seed"]), float(g[f"{name}_secs"]))
+        buf = torch.zeros(1, 480000)
+        buf[0, : len(a)] = torch.from_numpy(a)
+        mel = e.logmel(buf.cuda(), n_samples=[len(a)]).cpu()[0]
+        ref = oracle.window_mel(oracle.log_mel(torch.from_numpy(a)))
+        assert (mel - ref).abs().max() < MEL_TOL
+        assert np.abs(mel[:, ::37].numpy() - g[f"{name}_mel"]).max() < MEL_TOL
+
+
+def test_logmel_ragged_batch_and_window_offset(small_f32):
+    e, _, _ = small_f32
+    lens = [480000, 123456, 16000]
+    buf = torch.zeros(3, 480000)
+    clips = [synth.clip(20 + i, n / 16000) for i, n in enumerate(lens)]
+    for i, c in enumerate(clips):
+        buf[i, : len(c)] = torch.from_numpy(c)
+    offs = [0, 250, 40]
+    mel = e.logmel(buf.cuda(), n_samples=lens, frame_offset=offs).cpu()
+    for i, c in enumerate(clips):
+        ref = oracle.window_mel(oracle.log_mel(torch.from_numpy(c)), offs[i])
+        assert (mel[i] - ref).abs().max() < MEL_TOL
+        n_valid = max(0, lens[i] // 160 - offs[i])
+        assert torch.all(mel[i, :, n_valid:] == -1.5)
+
+
+# ----------------------------------------------------------------------- encoder
+def _encoder_case(e, dims, sd, seeds, tol, golden=None):
+    audio = synth.clips(seeds)
+    mel_ref = _oracle_mel(audio)
+    xa_ref = oracle.encoder(sd, mel_ref, dims.n_audio_layer, dims.n_audio_head)
+    mel = e.logmel(torch.from_numpy(audio).cuda())
+    xa = e.encode(mel).float().cpu()
+    rel = (xa - xa_ref).norm() / xa_ref.norm()
+    assert rel < tol, rel
+    if golden is not None:
+        gx = torch.from_numpy(golden["xa"])
+        assert (xa[:, ::50] - gx).norm() / gx.norm() < tol
+    return xa_ref
+
+
+def test_encoder_f32(small_f32, golden_dir):
+    e, dims, sd = small_f32
+    g = np.load(os.path.join(golden_dir, "model_test_small.npz"))
+    _encoder_case(e, dims, sd, [int(s) for s in g["clip_seeds"]], F32_ENC_TOL, g)
+
+
+def test_encoder_bf16(small_bf16, golden_dir):
+    e, dims, sd = small_bf16
+    g = np.load(os.path.join(golden_dir, "model_test_small.npz"))
+    _encoder_case(e, dims, sd, [int(s) for s in g["clip_seeds"]], BF16_ENC_TOL, g)
+
+
+# ----------------------------------------------------------------------- decoder
+def _greedy(e, dims, xa, prompt, slots, n_steps, teacher=None):
+    """Prefill + n_steps; returns (tokens [B, n_steps], logits [B, n_steps, V]).
+    With ``teacher`` ([B, n_steps]) the fed tokens are the teacher's."""
+    eot = min(TOK_EOT, dims.n_vocab - 1)
+    logits = e.prefill(xa, slots, [list(map(int, p)) for p in prompt])
+    toks, kept = [], []
+    for step in range(n_steps):
+        kept.append(logits.cpu())
+        lg = logits.clone()
+        lg[:, eot] = float("-inf")
+        nxt = lg.argmax(-1)
+        toks.append(nxt.cpu())
+        feed = nxt if teacher is None else torch.as_tensor(teacher[:, step]).cuda()
+        _, logits = e.decode_step(feed, slots, rules=None, want_logits=True)
+    return torch.stack(toks, 1), torch.stack(kept, 1)
+
+
+def test_decoder_f32_tokens_identical_to_reference(small_f32, golden_dir):
+    e, dims, sd = small_f32
+    g = np.load(os.path.join(golden_dir, "model_test_small.npz"))
+    audio = synth.clips([int(s) for s in g["clip_seeds"]])
+    xa = e.encode(e.logmel(torch.from_numpy(audio).cuda()))
+    B, n_steps = g["tokens"].shape
+    slots = list(range(1, B + 1))
+    toks, logits = _greedy(e, dims, xa, g["prompt"], slots, n_steps)
+    assert np.array_equal(toks.numpy(), g["tokens"])
+    ref = torch.from_numpy(g["logits"])
+    got = logits[:, :, :: int(g["logit_stride"])]
+    assert (got - ref).abs().max() < F32_LOGIT_TOL * ref.pow(2).mean().sqrt()
+    sl = e.seq_lens()
+    assert sl[1: B + 1] == [int(v) for v in g["final_seq_lens"][1: B + 1]]
+
+
+def test_decoder_bf16_teacher_forced_logits(small_bf16, golden_dir):
+    e, dims, sd = small_bf16
+    g = np.load(os.path.join(golden_dir, "model_test_small.npz"))
+    audio = synth.clips([int(s) for s in g["clip_seeds"]])
+    xa = e.encode(e.logmel(torch.from_numpy(audio).cuda()))
+    B, n_steps = g["tokens"].shape
+    _, logits = _greedy(e, dims, xa, g["prompt"], list(range(1, B + 1)), n_steps, teacher=g["tokens"])
+    ref = torch.from_numpy(g["logits"])
+    got = logits[:, :, :: int(g["logit_stride"])]
+    assert (got - ref).abs().max() < BF16_LOGIT_TOL * ref.pow(2).mean().sqrt()
+
+
+def test_ragged_rows_against_oracle(small_f32):
+    """Slots at different depths with prompts of different lengths, decoded in
+    one packed step per iteration, against the oracle run slot by slot."""
+    e, dims, sd = small_f32
+    rng = np.random.default_rng(7)
+    audio = synth.clips([11, 12])
+    mel = _oracle_mel(audio)
+    xa_ref = oracle.encoder(sd, mel, dims.n_audio_layer, dims.n_audio_head)
+    xa = xa_ref.cuda()
+    prompts = [list(rng.integers(0, 50000, 9)), list(rng.integers(0, 50000, 4))]
+    slots = [4, 2]
+    dec = oracle.SlotDecoder(sd, dims.n_text_layer, dims.n_text_head, 6, dims.n_text_ctx)
+    dec.set_cross(xa_ref, slots)
+    dec.reset(slots)
+    ref_last = [dec.forward(torch.tensor([p]), [s])[0, -1] for p, s in zip(prompts, slots)]
+    got = e.prefill(xa, slots, prompts).cpu()
+    rms = torch.stack(ref_last).pow(2).mean().sqrt()
+    assert (got - torch.stack(ref_last)).abs().max() < F32_LOGIT_TOL * rms
+    assert [e.seq_lens()[s] for s in slots] == [9, 4]
+    cur = got.argmax(-1)
+    for _ in range(5):
+        ref = torch.stack([dec.forward(cur[i].view(1, 1), [s])[0, 0] for i, s in enumerate(slots)])
+        nxt, lg = e.decode_step(cur, slots, want_logits=True)
+        assert (lg.cpu() - ref).abs().max() < F32_LOGIT_TOL * rms
+        assert torch.equal(nxt.cpu().long(), ref.argmax(-1))
+        cur = ref.argmax(-1)
+    assert [e.seq_lens()[s] for s in slots] == [14, 9]
+    # a slot that was reset starts again at position 0 and leaves the other alone
+    e.slot_reset([2])
+    assert e.seq_lens()[2] == 0 and e.seq_lens()[4] == 14
+
+
+# ------------------------------------------------------------------------- rules
+def test_rules_argmax_bit_exact():
+    from whisperdrz_b200.engine import Engine
+    dims = ModelDimensions.from_name("test-tiny")
+    sd = init_state_dict(dims, 0)
+    V = dims.n_vocab
+    g = torch.Generator().manual_seed(3)
+    tables = torch.rand(5, V, generator=g) < 0.3
+    e = Engine(dims, sd, dtype=torch.float32, n_slots=16, max_clips=1, tables=tables)
+    logits = torch.randn(12, V, generator=g) * 3
+    logits[5, 100] = logits[5, 7] = 50.0            # tie -> lowest id
+    rules = [
+        {},
+        {"table_bits": 0b10101},
+        {"mode": oracle.MODE_ALL_EXCEPT_TABLE, "arg0": 1, "table_bits": 0b1},
+        {"mode": oracle.MODE_ALL_EXCEPT_RANGE, "arg0": 900, "arg1": 1200},
+        {"mode": oracle.MODE_ALL, "clear_ids": [3, 77, 1500]},
+        {},
+        {"prefix_begin": 0, "prefix_end": 1000, "set_ids": [1001, 1002], "clear_ids": [5]},
+        {"forced_id": 42},
+        {"pen_ids": [int(logits[8].argmax())]},
+        {"pen_ids": list(map(int, logits[9].topk(10).indices))},
+        {"table_bits": 0b11111, "pen_ids": [1, 2, 3]},
+        {"mode": oracle.MODE_ALL},                   # everything blocked: plain argmax of shifted row
+    ]
+    ref = oracle.rules_argmax(logits, rules, tables)
+    got = e.rules_argmax(logits.cuda(), rules).cpu().long()
+    assert torch.equal(got, ref)
+    ref2 = oracle.rules_argmax(logits, rules, tables, penalty=False)
+    got2 = e.rules_argmax(logits.cuda(), rules, penalty=False).cpu().long()
+    assert torch.equal(got2, ref2)
+    assert got[5] == 7
+    e.device_status()
+    # a NaN row is reported, not silently argmax-ed
+    bad = logits.clone()
+    bad[0, 10] = float("nan")
+    out = e.rules_argmax(bad.cuda(), rules).cpu()
+    assert out[0] == -1
+    from whisperdrz_b200.capi import WdzError
+    with pytest.raises(WdzError):
+        e.device_status()
+    e.device_status()  # cleared by the read
+    e.close()
+
+
+def test_capacity_and_argument_errors(small_f32):
+    from whisperdrz_b200.capi import WdzError
+    e, dims, _ = small_f32
+    with pytest.raises(WdzError):
+        e.encode(torch.zeros(3, dims.n_mels, 3000))          # > max_clips
+    with pytest.raises(WdzError):
+        e.decode_step([1] * 100, [0] * 100)                  # > max_rows
+    with pytest.raises(ValueError):
+        e.logmel(torch.zeros(1, 300))                        # too short to reflect-pad

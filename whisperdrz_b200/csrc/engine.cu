@@ -1,0 +1,664 @@
+// libwdz.so: the engine behind the C ABI of include/wdz.h.
+//
+// The engine owns no device memory: weights, KV caches and tables are lent by
+// the host (wdz_bind) and all scratch comes from one caller-provided workspace
+// (wdz_set_workspace) carved up here.  Every entry point only enqueues
+// kernels on the caller's stream.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/wdz.h"
+#include "attention.cuh"
+#include "common.cuh"
+#include "elementwise.cuh"
+#include "gemm_simt.cuh"
+#include "logmel.cuh"
+#include "rules.cuh"
+#ifdef WDZ_WITH_TC
+#include "gemm_tc.cuh"
+#endif
+
+using namespace wdz;
+
+namespace {
+
+struct Bound { const void* ptr; int64_t numel; };
+
+struct LayerW {
+  const void *ln1_w, *ln1_b, *qkv_w, *qkv_b, *out_w, *out_b;
+  const void *lnx_w, *lnx_b, *xq_w, *xq_b, *xout_w, *xout_b;  // decoder cross-attention
+  const void *ln2_w, *ln2_b, *fc1_w, *fc1_b, *fc2_w, *fc2_b;
+};
+
+}  // namespace
+
+struct wdz_engine {
+  wdz_config cfg{};
+  std::string err;
+  std::unordered_map<std::string, Bound> bound;
+  bool finalized = false;
+  int device = 0;
+  int sm_count = 148;
+  size_t esz = 2;
+
+  // resolved tensors
+  const void *conv1_w = nullptr, *conv1_b = nullptr, *conv2_w = nullptr, *conv2_b = nullptr;
+  const float* enc_pos = nullptr;
+  const void *ln_post_w = nullptr, *ln_post_b = nullptr;
+  std::vector<LayerW> enc, dec;
+  const void *tok_emb = nullptr, *dec_pos = nullptr, *dec_ln_w = nullptr, *dec_ln_b = nullptr;
+  const void *xkv_w = nullptr, *xkv_b = nullptr;
+  void *self_k = nullptr, *self_v = nullptr, *cross_k = nullptr, *cross_v = nullptr;
+  int* seq_lens = nullptr;
+  const uint32_t* tables = nullptr;
+  MelTables mel{};
+
+  // workspace
+  char* ws = nullptr;
+  size_t ws_bytes = 0;
+  float* mel_raw = nullptr; int* clipmax = nullptr;
+  void *col1 = nullptr, *h1p = nullptr, *xn = nullptr, *qkv = nullptr, *ao = nullptr, *hid = nullptr;
+  float* x = nullptr;
+  float *dx = nullptr, *dxn = nullptr, *dqkv = nullptr, *dao = nullptr, *dq = nullptr, *dh = nullptr;
+  float *part_o = nullptr, *part_ml = nullptr, *logits = nullptr;
+  int* dpos = nullptr;
+  DevStatus* status = nullptr;
+  int64_t part_entries = 0;
+  int max_emit = 0;
+  int last_emit = 0;  // logit rows held from the last forward
+
+  int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    err = buf;
+    return code;
+  }
+};
+
+namespace {
+
+#define WDZ_LAUNCH_CHECK(e, what)                                                   \
+  do {                                                                              \
+    cudaError_t _c = cudaGetLastError();                                            \
+    if (_c != cudaSuccess) return (e)->fail(WDZ_ECUDA, "%s: %s", what, cudaGetErrorString(_c)); \
+  } while (0)
+
+size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+
+int64_t part_entries_for(const wdz_config& c) {
+  int64_t a = 4ll * c.max_rows, b = (int64_t)c.max_rows + 512;
+  return a > b ? a : b;
+}
+
+// Carves the workspace; with base == nullptr only measures.
+size_t carve(wdz_engine* e, char* base) {
+  const wdz_config& c = e->cfg;
+  const size_t es = e->esz;
+  size_t off = 0;
+  auto take = [&](size_t bytes) -> char* {
+    char* p = base ? base + off : nullptr;
+    off += align_up(bytes);
+    return p;
+  };
+  const int64_t B = c.max_clips, Ta = c.n_audio_ctx, da = c.n_audio_state, R = c.max_rows, dt = c.n_text_state;
+  const int H = c.n_text_head;
+  e->status = (DevStatus*)take(sizeof(DevStatus));
+  e->mel_raw = (float*)take(sizeof(float) * B * c.n_mels * MEL_MAX_FRAMES);
+  e->clipmax = (int*)take(sizeof(int) * B);
+  e->col1 = take(es * B * 2 * Ta * 3 * c.n_mels);
+  e->h1p = take(es * B * (2 * Ta + 2) * da);
+  e->x = (float*)take(sizeof(float) * B * Ta * da);
+  e->xn = take(es * B * Ta * da);
+  e->qkv = take(es * B * Ta * 3 * da);
+  e->ao = take(es * B * Ta * da);
+  e->hid = take(es * B * Ta * 4 * da);
+  e->dx = (float*)take(sizeof(float) * R * dt);
+  e->dxn = (float*)take(sizeof(float) * R * dt);
+  e->dqkv = (float*)take(sizeof(float) * R * 3 * dt);
+  e->dao = (float*)take(sizeof(float) * R * dt);
+  e->dq = (float*)take(sizeof(float) * R * dt);
+  e->dh = (float*)take(sizeof(float) * R * 4 * dt);
+  e->dpos = (int*)take(sizeof(int) * R);
+  e->part_entries = part_entries_for(c);
+  e->part_o = (float*)take(sizeof(float) * e->part_entries * H * HD);
+  e->part_ml = (float*)take(sizeof(float) * e->part_entries * H * 2);
+  e->max_emit = c.max_rows < c.n_slots ? c.max_rows : c.n_slots;
+  if (e->max_emit < 1) e->max_emit = 1;
+  e->logits = (float*)take(sizeof(float) * (int64_t)e->max_emit * c.n_vocab);
+  return off;
+}
+
+// ---- GEMM dispatch ---------------------------------------------------------
+template <typename TA, typename TW, typename TO>
+int launch_gemm_tile(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s) {
+  dim3 grid((p.N + 63) / 64, (p.M + 63) / 64);
+  switch (epi) {
+    case EPI_STORE: gemm_tile_kernel<TA, TW, TO, EPI_STORE><<<grid, 256, 0, s>>>(p); break;
+    case EPI_GELU: gemm_tile_kernel<TA, TW, TO, EPI_GELU><<<grid, 256, 0, s>>>(p); break;
+    case EPI_RESID: gemm_tile_kernel<TA, TW, TO, EPI_RESID><<<grid, 256, 0, s>>>(p); break;
+    case EPI_GELU_POS: gemm_tile_kernel<TA, TW, TO, EPI_GELU_POS><<<grid, 256, 0, s>>>(p); break;
+    case EPI_CROSS_KV: gemm_tile_kernel<TA, TW, TO, EPI_CROSS_KV><<<grid, 256, 0, s>>>(p); break;
+    default: return e->fail(WDZ_EINVAL, "bad epilogue %d", epi);
+  }
+  WDZ_LAUNCH_CHECK(e, "gemm_tile");
+  return WDZ_OK;
+}
+
+GemmParams dense_params(const void* A, int64_t lda, const void* W, const void* bias, void* C, int64_t ldc,
+                        int M, int N, int K) {
+  GemmParams p{};
+  p.A = A; p.W = W; p.bias = bias; p.C = C;
+  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc;
+  p.a_rpb = M > 0 ? M : 1; p.a_bstride = 0; p.c_rpb = M > 0 ? M : 1; p.c_bstride = 0;
+  return p;
+}
+
+// Encoder-side product (A and outputs in T).  The tensor-core kernel takes the
+// bf16 case when it is compiled in and not disabled.
+template <typename T>
+int enc_gemm(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s) {
+#ifdef WDZ_WITH_TC
+  if (sizeof(T) == 2 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) {
+    int rc = gemm_tc_launch(e, epi, p, s);
+    if (rc != 1) return rc;  // 1 = shape not supported, fall through
+  }
+#endif
+  return launch_gemm_tile<T, T, T>(e, epi, p, s);
+}
+
+template <typename T, int EPI>
+int launch_gemv(wdz_engine* e, const GemvParams& p, cudaStream_t s) {
+  // few columns per warp when N is small so that every SM streams weights
+  const int warps_needed_1 = p.N;
+  if (warps_needed_1 <= 8 * 2 * e->sm_count * 2) {
+    gemv_rows_kernel<T, EPI, 1><<<(p.N + 7) / 8, 256, 0, s>>>(p);
+  } else if (p.N <= 8 * 4 * e->sm_count * 4) {
+    gemv_rows_kernel<T, EPI, 2><<<(p.N + 15) / 16, 256, 0, s>>>(p);
+  } else {
+    gemv_rows_kernel<T, EPI, 4><<<(p.N + 31) / 32, 256, 0, s>>>(p);
+  }
+  WDZ_LAUNCH_CHECK(e, "gemv_rows");
+  return WDZ_OK;
+}
+
+// Decode-side product: x f32 [M, K] -> y f32 [M, N].
+template <typename T>
+int dec_gemm(wdz_engine* e, int epi, const float* x, int64_t ldx, const void* W, const void* bias,
+             float* y, int64_t ldy, int M, int N, int K, const int* row_idx, cudaStream_t s) {
+  if (M <= 64 || row_idx) {
+    GemvParams p{x, W, bias, y, M, N, K, ldx, ldy, row_idx};
+    switch (epi) {
+      case EPI_STORE: return launch_gemv<T, EPI_STORE>(e, p, s);
+      case EPI_GELU: return launch_gemv<T, EPI_GELU>(e, p, s);
+      case EPI_RESID: return launch_gemv<T, EPI_RESID>(e, p, s);
+      default: return e->fail(WDZ_EINVAL, "bad decode epilogue %d", epi);
+    }
+  }
+  GemmParams p = dense_params(x, ldx, W, bias, y, ldy, M, N, K);
+  return launch_gemm_tile<float, T, float>(e, epi, p, s);
+}
+
+template <typename TP, typename TO>
+int launch_ln(wdz_engine* e, const float* x, int64_t ldx, const int* row_idx, const void* g, const void* b,
+              TO* y, int64_t ldy, int rows, int d, cudaStream_t s) {
+  if (rows <= 0) return WDZ_OK;
+  layernorm_kernel<TP, TO><<<(rows + 7) / 8, 256, 0, s>>>(x, ldx, row_idx, (const TP*)g, (const TP*)b, y, ldy, rows, d);
+  WDZ_LAUNCH_CHECK(e, "layernorm");
+  return WDZ_OK;
+}
+
+// ---- encoder ---------------------------------------------------------------
+template <typename T>
+int encode_impl(wdz_engine* e, const float* mel, int B, void* xa_out, cudaStream_t s) {
+  const wdz_config& c = e->cfg;
+  const int Ta = c.n_audio_ctx, frames = 2 * Ta, d = c.n_audio_state, H = c.n_audio_head;
+  const int M = B * Ta;
+  int rc;
+  // conv1 as a product over the tap-major im2col operand
+  im2col_conv1_kernel<T><<<dim3((frames + 31) / 32, B), 256, sizeof(float) * c.n_mels * 35, s>>>(
+      mel, (T*)e->col1, c.n_mels, frames);
+  WDZ_LAUNCH_CHECK(e, "im2col");
+  const int64_t h1_b = (int64_t)(frames + 2) * d;  // one zero row before and after each window
+  zero_rows_kernel<T><<<B, 256, 0, s>>>((T*)e->h1p, h1_b, 0, d, B);
+  zero_rows_kernel<T><<<B, 256, 0, s>>>((T*)e->h1p, h1_b, (int64_t)(frames + 1) * d, d, B);
+  WDZ_LAUNCH_CHECK(e, "zero_rows");
+  {
+    GemmParams p = dense_params(e->col1, 3 * c.n_mels, e->conv1_w, e->conv1_b, (T*)e->h1p + d, d,
+                                B * frames, d, 3 * c.n_mels);
+    p.c_rpb = frames; p.c_bstride = h1_b;
+    if ((rc = enc_gemm<T>(e, EPI_GELU, p, s))) return rc;
+  }
+  // conv2 (stride 2): row (b, t) of the operand is the contiguous span
+  // h1p[b, 2t .. 2t+2, :] of the padded conv1 output, so no im2col is needed.
+  {
+    GemmParams p = dense_params(e->h1p, 2 * d, e->conv2_w, e->conv2_b, e->x, d, M, d, 3 * d);
+    p.a_rpb = Ta; p.a_bstride = h1_b;
+    p.pos = e->enc_pos;
+    if ((rc = enc_gemm<T>(e, EPI_GELU_POS, p, s))) return rc;
+  }
+  for (int l = 0; l < c.n_audio_layer; ++l) {
+    const LayerW& w = e->enc[l];
+    if ((rc = launch_ln<T, T>(e, e->x, d, nullptr, w.ln1_w, w.ln1_b, (T*)e->xn, d, M, d, s))) return rc;
+    if ((rc = enc_gemm<T>(e, EPI_STORE, dense_params(e->xn, d, w.qkv_w, w.qkv_b, e->qkv, 3 * d, M, 3 * d, d), s))) return rc;
+    attn_enc_simt_kernel<T><<<dim3((Ta + 63) / 64, H, B), 256, attn_enc_simt_smem(), s>>>(
+        (const T*)e->qkv, (T*)e->ao, Ta, d);
+    WDZ_LAUNCH_CHECK(e, "attn_enc");
+    if ((rc = enc_gemm<T>(e, EPI_RESID, dense_params(e->ao, d, w.out_w, w.out_b, e->x, d, M, d, d), s))) return rc;
+    if ((rc = launch_ln<T, T>(e, e->x, d, nullptr, w.ln2_w, w.ln2_b, (T*)e->xn, d, M, d, s))) return rc;
+    if ((rc = enc_gemm<T>(e, EPI_GELU, dense_params(e->xn, d, w.fc1_w, w.fc1_b, e->hid, 4 * d, M, 4 * d, d), s))) return rc;
+    if ((rc = enc_gemm<T>(e, EPI_RESID, dense_params(e->hid, 4 * d, w.fc2_w, w.fc2_b, e->x, d, M, d, 4 * d), s))) return rc;
+  }
+  return launch_ln<T, T>(e, e->x, d, nullptr, e->ln_post_w, e->ln_post_b, (T*)xa_out, d, M, d, s);
+}
+
+template <typename T>
+int cross_kv_impl(wdz_engine* e, const void* xa, const int* slot_ids, int B, cudaStream_t s) {
+  const wdz_config& c = e->cfg;
+  const int d = c.n_text_state;
+  GemmParams p = dense_params(xa, c.n_audio_state, e->xkv_w, e->xkv_b, nullptr, 0, B * c.n_audio_ctx,
+                              c.n_text_layer * 2 * d, c.n_audio_state);
+  p.cache_k = e->cross_k; p.cache_v = e->cross_v; p.slot_ids = slot_ids;
+  p.n_slots = c.n_slots; p.T = c.n_audio_ctx; p.d = d;
+  return enc_gemm<T>(e, EPI_CROSS_KV, p, s);
+}
+
+// ---- decoder ---------------------------------------------------------------
+template <typename T>
+int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool cross, cudaStream_t s) {
+  const int H = e->cfg.n_text_head;
+  int splits;
+  if (cross) {
+    splits = (3 * e->sm_count + rows - 1) / rows;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    p.chunk = ((max_len + splits - 1) / splits + 7) / 8 * 8;
+  } else {
+    p.chunk = 128;
+  }
+  splits = (max_len + p.chunk - 1) / p.chunk;
+  if ((int64_t)rows * splits > e->part_entries)
+    return e->fail(WDZ_ECAPACITY, "attention partials: %d rows x %d splits exceed the workspace", rows, splits);
+  p.max_splits = splits;
+  attn_dec_kernel<T><<<dim3(splits, rows), H * 32, 0, s>>>(p);
+  attn_dec_combine_kernel<<<rows, H * 32, 0, s>>>(p);
+  WDZ_LAUNCH_CHECK(e, "attn_dec");
+  return WDZ_OK;
+}
+
+// tokens/slots/positions: device int32 [n].  Logits of the emit rows land in e->logits.
+template <typename T>
+int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const int* positions, int n,
+                      const int* emit_rows, int n_emit, cudaStream_t s) {
+  const wdz_config& c = e->cfg;
+  const int d = c.n_text_state, H = c.n_text_head;
+  int rc;
+  embed_kernel<T><<<n, 256, 0, s>>>(tokens, positions, (const T*)e->tok_emb, (const T*)e->dec_pos, e->dx, n, d,
+                                     c.n_vocab, c.n_text_ctx);
+  WDZ_LAUNCH_CHECK(e, "embed");
+  AttnDecParams ap{};
+  ap.n_slots = c.n_slots; ap.d = d; ap.slots = slots;
+  ap.part_o = e->part_o; ap.part_ml = e->part_ml; ap.out = e->dao; ap.ldo = d;
+  for (int l = 0; l < c.n_text_layer; ++l) {
+    const LayerW& w = e->dec[l];
+    if ((rc = launch_ln<T, float>(e, e->dx, d, nullptr, w.ln1_w, w.ln1_b, e->dxn, d, n, d, s))) return rc;
+    if ((rc = dec_gemm<T>(e, EPI_STORE, e->dxn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d, nullptr, s))) return rc;
+    kv_append_kernel<T><<<n, 256, 0, s>>>(e->dqkv, slots, positions, (T*)e->self_k, (T*)e->self_v, l, c.n_slots,
+                                           c.max_tokens, d, n);
+    WDZ_LAUNCH_CHECK(e, "kv_append");
+    ap.layer = l;
+    ap.q = e->dqkv; ap.ldq = 3 * d; ap.cache_k = e->self_k; ap.cache_v = e->self_v; ap.S = c.max_tokens;
+    ap.positions = positions; ap.fixed_len = 0;
+    if ((rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
+    if ((rc = dec_gemm<T>(e, EPI_RESID, e->dao, d, w.out_w, w.out_b, e->dx, d, n, d, d, nullptr, s))) return rc;
+
+    if ((rc = launch_ln<T, float>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, e->dxn, d, n, d, s))) return rc;
+    if ((rc = dec_gemm<T>(e, EPI_STORE, e->dxn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, nullptr, s))) return rc;
+    ap.q = e->dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
+    ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
+    if ((rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
+    if ((rc = dec_gemm<T>(e, EPI_RESID, e->dao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d, nullptr, s))) return rc;
+
+    if ((rc = launch_ln<T, float>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, e->dxn, d, n, d, s))) return rc;
+    if ((rc = dec_gemm<T>(e, EPI_GELU, e->dxn, d, w.fc1_w, w.fc1_b, e->dh, 4 * d, n, 4 * d, d, nullptr, s))) return rc;
+    if ((rc = dec_gemm<T>(e, EPI_RESID, e->dh, 4 * d, w.fc2_w, w.fc2_b, e->dx, d, n, d, 4 * d, nullptr, s))) return rc;
+  }
+  bump_seqlens_kernel<<<(n + 255) / 256, 256, 0, s>>>(slots, positions, e->seq_lens, n, c.n_slots);
+  WDZ_LAUNCH_CHECK(e, "bump_seqlens");
+  // final LayerNorm on the emit rows only, then the tied LM head (model.py:609-613)
+  if ((rc = launch_ln<T, float>(e, e->dx, d, emit_rows, e->dec_ln_w, e->dec_ln_b, e->dxn, d, n_emit, d, s))) return rc;
+  if ((rc = dec_gemm<T>(e, EPI_STORE, e->dxn, d, e->tok_emb, nullptr, e->logits, c.n_vocab, n_emit, c.n_vocab, d,
+                        nullptr, s))) return rc;
+  e->last_emit = n_emit;
+  return WDZ_OK;
+}
+
+int check_ready(wdz_engine* e) {
+  if (!e) return WDZ_EINVAL;
+  if (!e->finalized) return e->fail(WDZ_ESTATE, "engine not finalized");
+  if (!e->ws) return e->fail(WDZ_ENOMEM, "no workspace set");
+  return WDZ_OK;
+}
+
+int rules_launch(wdz_engine* e, const float* logits, const int* row_idx, const wdz_rule_desc* rules, int n,
+                 int penalty, int* out, cudaStream_t s) {
+  if (n <= 0) return WDZ_OK;
+  const int V = e->cfg.n_vocab;
+  rules_argmax_kernel<<<n, 1024, 0, s>>>(logits, V, row_idx, rules, e->tables, (V + 31) / 32, V, penalty, out,
+                                         e->status);
+  WDZ_LAUNCH_CHECK(e, "rules_argmax");
+  return WDZ_OK;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+extern "C" {
+
+const char* wdz_version(void) { return "wdz 0.1 (sm_100a)"; }
+
+int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
+  if (!cfg || !out) return WDZ_EINVAL;
+  *out = nullptr;
+  const wdz_config& c = *cfg;
+  if (c.dtype != WDZ_F32 && c.dtype != WDZ_BF16) return WDZ_EINVAL;
+  if (c.n_audio_state != c.n_audio_head * HD || c.n_text_state != c.n_text_head * HD) return WDZ_EINVAL;
+  if (c.n_audio_head > 32 || c.n_text_head > 32 || c.n_mels > 160 || c.n_mels < 1) return WDZ_EINVAL;
+  if (c.n_slots < 1 || c.max_tokens < 1 || c.max_clips < 1 || c.max_rows < 1) return WDZ_EINVAL;
+  if (c.n_audio_layer < 1 || c.n_text_layer < 1 || c.n_vocab < 1 || c.max_tokens > c.n_text_ctx) return WDZ_EINVAL;
+  wdz_engine* e = new wdz_engine();
+  e->cfg = c;
+  e->esz = c.dtype == WDZ_BF16 ? 2 : 4;
+  e->enc.resize(c.n_audio_layer);
+  e->dec.resize(c.n_text_layer);
+  if (cudaGetDevice(&e->device) == cudaSuccess) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device) == cudaSuccess && sms > 0)
+      e->sm_count = sms;
+  } else {
+    cudaGetLastError();
+  }
+  *out = e;
+  return WDZ_OK;
+}
+
+int wdz_engine_destroy(wdz_engine* e) {
+  delete e;
+  return WDZ_OK;
+}
+
+const char* wdz_last_error(const wdz_engine* e) { return e ? e->err.c_str() : "null engine"; }
+
+int wdz_workspace_bytes(const wdz_engine* e, size_t* out_bytes) {
+  if (!e || !out_bytes) return WDZ_EINVAL;
+  wdz_engine tmp;
+  tmp.cfg = e->cfg;
+  tmp.esz = e->esz;
+  *out_bytes = carve(&tmp, nullptr) + 256;
+  return WDZ_OK;
+}
+
+int wdz_set_workspace(wdz_engine* e, void* dev, size_t bytes) {
+  if (!e || !dev) return WDZ_EINVAL;
+  size_t need = 0;
+  wdz_workspace_bytes(e, &need);
+  if (bytes < need) return e->fail(WDZ_ENOMEM, "workspace of %zu bytes, need %zu", bytes, need);
+  char* base = (char*)align_up((size_t)dev);
+  carve(e, base);
+  e->ws = base;
+  e->ws_bytes = bytes;
+  if (cudaMemset(e->status, 0, sizeof(DevStatus)) != cudaSuccess) {
+    cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "cannot clear the status word");
+  }
+  return WDZ_OK;
+}
+
+int wdz_bind(wdz_engine* e, const char* name, const void* dev, int64_t numel) {
+  if (!e || !name || !dev || numel <= 0) return WDZ_EINVAL;
+  e->bound[name] = Bound{dev, numel};
+  e->finalized = false;
+  return WDZ_OK;
+}
+
+int wdz_finalize(wdz_engine* e) {
+  if (!e) return WDZ_EINVAL;
+  const wdz_config& c = e->cfg;
+  int rc = WDZ_OK;
+  auto get = [&](const std::string& name, int64_t numel, bool optional = false) -> const void* {
+    auto it = e->bound.find(name);
+    if (it == e->bound.end()) {
+      if (!optional && rc == WDZ_OK) rc = e->fail(WDZ_ESTATE, "tensor '%s' was never bound", name.c_str());
+      return nullptr;
+    }
+    if (it->second.numel != numel) {
+      if (rc == WDZ_OK)
+        rc = e->fail(WDZ_EINVAL, "tensor '%s' has %lld elements, expected %lld", name.c_str(),
+                     (long long)it->second.numel, (long long)numel);
+      return nullptr;
+    }
+    return it->second.ptr;
+  };
+  const int64_t da = c.n_audio_state, dt = c.n_text_state;
+  e->conv1_w = get("encoder.conv1.weight", da * 3 * c.n_mels);
+  e->conv1_b = get("encoder.conv1.bias", da);
+  e->conv2_w = get("encoder.conv2.weight", da * 3 * da);
+  e->conv2_b = get("encoder.conv2.bias", da);
+  e->enc_pos = (const float*)get("encoder.positional_embedding", (int64_t)c.n_audio_ctx * da);
+  e->ln_post_w = get("encoder.ln_post.weight", da);
+  e->ln_post_b = get("encoder.ln_post.bias", da);
+  auto block = [&](const std::string& p, LayerW& w, int64_t d, bool cross) {
+    w.ln1_w = get(p + ".attn_ln.weight", d); w.ln1_b = get(p + ".attn_ln.bias", d);
+    w.qkv_w = get(p + ".attn.qkv.weight", 3 * d * d); w.qkv_b = get(p + ".attn.qkv.bias", 3 * d);
+    w.out_w = get(p + ".attn.out.weight", d * d); w.out_b = get(p + ".attn.out.bias", d);
+    if (cross) {
+      w.lnx_w = get(p + ".cross_attn_ln.weight", d); w.lnx_b = get(p + ".cross_attn_ln.bias", d);
+      w.xq_w = get(p + ".cross_attn.query.weight", d * d); w.xq_b = get(p + ".cross_attn.query.bias", d);
+      w.xout_w = get(p + ".cross_attn.out.weight", d * d); w.xout_b = get(p + ".cross_attn.out.bias", d);
+    }
+    w.ln2_w = get(p + ".mlp_ln.weight", d); w.ln2_b = get(p + ".mlp_ln.bias", d);
+    w.fc1_w = get(p + ".mlp.0.weight", 4 * d * d); w.fc1_b = get(p + ".mlp.0.bias", 4 * d);
+    w.fc2_w = get(p + ".mlp.2.weight", 4 * d * d); w.fc2_b = get(p + ".mlp.2.bias", d);
+  };
+  for (int l = 0; l < c.n_audio_layer; ++l) block("encoder.blocks." + std::to_string(l), e->enc[l], da, false);
+  for (int l = 0; l < c.n_text_layer; ++l) block("decoder.blocks." + std::to_string(l), e->dec[l], dt, true);
+  e->tok_emb = get("decoder.token_embedding.weight", (int64_t)c.n_vocab * dt);
+  e->dec_pos = get("decoder.positional_embedding", (int64_t)c.n_text_ctx * dt);
+  e->dec_ln_w = get("decoder.ln.weight", dt);
+  e->dec_ln_b = get("decoder.ln.bias", dt);
+  e->xkv_w = get("decoder.cross_kv.weight", (int64_t)c.n_text_layer * 2 * dt * da);
+  e->xkv_b = get("decoder.cross_kv.bias", (int64_t)c.n_text_layer * 2 * dt);
+  const int64_t self_n = (int64_t)c.n_text_layer * c.n_slots * c.max_tokens * dt;
+  const int64_t cross_n = (int64_t)c.n_text_layer * c.n_slots * c.n_audio_ctx * dt;
+  e->self_k = (void*)get("cache.self_k", self_n);
+  e->self_v = (void*)get("cache.self_v", self_n);
+  e->cross_k = (void*)get("cache.cross_k", cross_n);
+  e->cross_v = (void*)get("cache.cross_v", cross_n);
+  e->seq_lens = (int*)get("cache.seq_lens", c.n_slots);
+  e->tables = (const uint32_t*)get("rules.tables", (int64_t)WDZ_MAX_TABLES * ((c.n_vocab + 31) / 32), true);
+  e->mel.twiddle = (const float2*)get("mel.twiddle", 2 * MEL_NFFT);
+  e->mel.window = (const float*)get("mel.window", MEL_NFFT);
+  e->mel.fb = (const float*)get("mel.fb", (int64_t)MEL_BINS * c.n_mels);
+  e->mel.band_lo = (const int*)get("mel.band_lo", c.n_mels);
+  e->mel.band_hi = (const int*)get("mel.band_hi", c.n_mels);
+  if (rc != WDZ_OK) return rc;
+
+  cudaError_t ce = cudaFuncSetAttribute(logmel_raw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)logmel_smem_bytes());
+  if (ce == cudaSuccess)
+    ce = cudaFuncSetAttribute(attn_enc_simt_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)attn_enc_simt_smem());
+  if (ce == cudaSuccess)
+    ce = cudaFuncSetAttribute(attn_enc_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)attn_enc_simt_smem());
+  if (ce != cudaSuccess) {
+    cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(ce));
+  }
+#ifdef WDZ_WITH_TC
+  if ((rc = gemm_tc_init(e)) != WDZ_OK) return rc;
+#endif
+  e->finalized = true;
+  return WDZ_OK;
+}
+
+int wdz_device_status(wdz_engine* e, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  DevStatus h{};
+  cudaStream_t st = (cudaStream_t)s;
+  if (cudaMemcpyAsync(&h, e->status, sizeof h, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "status read: %s", cudaGetErrorString(ce));
+  }
+  if (h.code != 0) {
+    cudaMemsetAsync(e->status, 0, sizeof(DevStatus), st);
+    return e->fail(h.code, "device reported status %d (detail %d)", h.code, h.detail);
+  }
+  return WDZ_OK;
+}
+
+int wdz_logmel(wdz_engine* e, const float* audio_dev, int64_t audio_stride, const int32_t* n_samples_dev,
+               const int32_t* frame_offset_dev, int B, float* mel_out_dev, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!audio_dev || !n_samples_dev || !mel_out_dev || B < 0) return e->fail(WDZ_EINVAL, "wdz_logmel: null argument");
+  if (B == 0) return WDZ_OK;
+  if (B > e->cfg.max_clips) return e->fail(WDZ_ECAPACITY, "wdz_logmel: %d clips > max_clips %d", B, e->cfg.max_clips);
+  cudaStream_t st = (cudaStream_t)s;
+  logmel_init_max_kernel<<<(B + 255) / 256, 256, 0, st>>>(e->clipmax, B);
+  logmel_raw_kernel<<<dim3((MEL_MAX_FRAMES + MEL_FT - 1) / MEL_FT, B), 256, logmel_smem_bytes(), st>>>(
+      audio_dev, audio_stride, n_samples_dev, e->mel, e->cfg.n_mels, e->mel_raw, e->clipmax);
+  logmel_finalize_kernel<<<dim3((MEL_MAX_FRAMES + 255) / 256, e->cfg.n_mels, B), 256, 0, st>>>(
+      e->mel_raw, e->clipmax, n_samples_dev, frame_offset_dev, e->cfg.n_mels, mel_out_dev);
+  WDZ_LAUNCH_CHECK(e, "logmel");
+  return WDZ_OK;
+}
+
+int wdz_encode(wdz_engine* e, const float* mel_dev, int B, void* xa_out_dev, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!mel_dev || !xa_out_dev || B < 0) return e->fail(WDZ_EINVAL, "wdz_encode: null argument");
+  if (B == 0) return WDZ_OK;
+  if (B > e->cfg.max_clips) return e->fail(WDZ_ECAPACITY, "wdz_encode: %d clips > max_clips %d", B, e->cfg.max_clips);
+  return e->cfg.dtype == WDZ_BF16 ? encode_impl<bf16>(e, mel_dev, B, xa_out_dev, (cudaStream_t)s)
+                                  : encode_impl<float>(e, mel_dev, B, xa_out_dev, (cudaStream_t)s);
+}
+
+int wdz_cross_kv(wdz_engine* e, const void* xa_dev, const int32_t* slot_ids_dev, int B, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!xa_dev || !slot_ids_dev || B < 0) return e->fail(WDZ_EINVAL, "wdz_cross_kv: null argument");
+  if (B == 0) return WDZ_OK;
+  if (B > e->cfg.max_clips) return e->fail(WDZ_ECAPACITY, "wdz_cross_kv: %d windows > max_clips %d", B, e->cfg.max_clips);
+  return e->cfg.dtype == WDZ_BF16 ? cross_kv_impl<bf16>(e, xa_dev, slot_ids_dev, B, (cudaStream_t)s)
+                                  : cross_kv_impl<float>(e, xa_dev, slot_ids_dev, B, (cudaStream_t)s);
+}
+
+int wdz_slot_reset(wdz_engine* e, const int32_t* slot_ids_dev, int n, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!slot_ids_dev || n < 0) return e->fail(WDZ_EINVAL, "wdz_slot_reset: null argument");
+  if (n == 0) return WDZ_OK;
+  reset_seqlens_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)s>>>(slot_ids_dev, e->seq_lens, n, e->cfg.n_slots);
+  WDZ_LAUNCH_CHECK(e, "slot_reset");
+  return WDZ_OK;
+}
+
+int wdz_slot_seqlens(wdz_engine* e, int32_t* out_host, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!out_host) return e->fail(WDZ_EINVAL, "wdz_slot_seqlens: null argument");
+  cudaStream_t st = (cudaStream_t)s;
+  if (cudaMemcpyAsync(out_host, e->seq_lens, sizeof(int) * e->cfg.n_slots, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "seq_lens read: %s", cudaGetErrorString(ce));
+  }
+  return WDZ_OK;
+}
+
+int wdz_forward_rows(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slot_ids_dev,
+                     const int32_t* positions_dev, int n, const int32_t* emit_rows_dev, int n_emit,
+                     float* logits_out_dev, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!tokens_dev || !slot_ids_dev || !positions_dev || n < 0) return e->fail(WDZ_EINVAL, "wdz_forward_rows: null argument");
+  if (n == 0) return WDZ_OK;
+  if (n > e->cfg.max_rows) return e->fail(WDZ_ECAPACITY, "wdz_forward_rows: %d rows > max_rows %d", n, e->cfg.max_rows);
+  if (!emit_rows_dev) n_emit = n;
+  if (n_emit < 0 || n_emit > e->max_emit)
+    return e->fail(WDZ_ECAPACITY, "wdz_forward_rows: %d logit rows > %d", n_emit, e->max_emit);
+  cudaStream_t st = (cudaStream_t)s;
+  rc = e->cfg.dtype == WDZ_BF16
+           ? forward_rows_impl<bf16>(e, tokens_dev, slot_ids_dev, positions_dev, n, emit_rows_dev, n_emit, st)
+           : forward_rows_impl<float>(e, tokens_dev, slot_ids_dev, positions_dev, n, emit_rows_dev, n_emit, st);
+  if (rc) return rc;
+  if (logits_out_dev && n_emit > 0) {
+    if (cudaMemcpyAsync(logits_out_dev, e->logits, sizeof(float) * (size_t)n_emit * e->cfg.n_vocab,
+                        cudaMemcpyDeviceToDevice, st) != cudaSuccess) {
+      cudaError_t ce = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "logits copy: %s", cudaGetErrorString(ce));
+    }
+  }
+  return WDZ_OK;
+}
+
+int wdz_prefill(wdz_engine* e, const void* xa_dev, const int32_t* window_slot_ids_dev, int B,
+                const int32_t* tokens_dev, const int32_t* slot_ids_dev, const int32_t* positions_dev, int n,
+                const int32_t* emit_rows_dev, int n_emit, float* logits_out_dev, wdz_stream s) {
+  int rc = wdz_cross_kv(e, xa_dev, window_slot_ids_dev, B, s);
+  if (rc) return rc;
+  if ((rc = wdz_slot_reset(e, window_slot_ids_dev, B, s))) return rc;
+  return wdz_forward_rows(e, tokens_dev, slot_ids_dev, positions_dev, n, emit_rows_dev, n_emit, logits_out_dev, s);
+}
+
+int wdz_decode_step(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slot_ids_dev, int n_active,
+                    const wdz_rule_desc* rules_dev, int32_t* next_tokens_out_dev, float* logits_out_dev,
+                    wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!tokens_dev || !slot_ids_dev || !next_tokens_out_dev || n_active < 0)
+    return e->fail(WDZ_EINVAL, "wdz_decode_step: null argument");
+  if (n_active == 0) return WDZ_OK;
+  if (n_active > e->cfg.max_rows || n_active > e->max_emit)
+    return e->fail(WDZ_ECAPACITY, "wdz_decode_step: %d rows > capacity %d", n_active,
+                   e->cfg.max_rows < e->max_emit ? e->cfg.max_rows : e->max_emit);
+  cudaStream_t st = (cudaStream_t)s;
+  positions_from_seqlens_kernel<<<(n_active + 255) / 256, 256, 0, st>>>(slot_ids_dev, e->seq_lens, e->dpos, n_active,
+                                                                        e->cfg.n_slots);
+  WDZ_LAUNCH_CHECK(e, "positions");
+  if ((rc = wdz_forward_rows(e, tokens_dev, slot_ids_dev, e->dpos, n_active, nullptr, n_active, logits_out_dev, s)))
+    return rc;
+  return rules_launch(e, e->logits, nullptr, rules_dev, n_active, 1, next_tokens_out_dev, st);
+}
+
+int wdz_reargmax(wdz_engine* e, const int32_t* rows_dev, const wdz_rule_desc* rules_dev, int n, int32_t* out_dev,
+                 wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!rows_dev || !out_dev || n < 0) return e->fail(WDZ_EINVAL, "wdz_reargmax: null argument");
+  if (n > e->last_emit) return e->fail(WDZ_EINVAL, "wdz_reargmax: %d rows but only %d logit rows are held", n, e->last_emit);
+  return rules_launch(e, e->logits, rows_dev, rules_dev, n, 0, out_dev, (cudaStream_t)s);
+}
+
+int wdz_rules_argmax(wdz_engine* e, const float* logits_dev, const wdz_rule_desc* rules_dev, int n,
+                     int apply_penalty, int32_t* out_dev, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!logits_dev || !out_dev || n < 0) return e->fail(WDZ_EINVAL, "wdz_rules_argmax: null argument");
+  return rules_launch(e, logits_dev, nullptr, rules_dev, n, apply_penalty ? 1 : 0, out_dev, (cudaStream_t)s);
+}
+
+}  // extern "C"
