@@ -1,0 +1,264 @@
+#!/usr/bin/env python
+"""Throughput of the transcription hot path on B200.
+
+One step = one pass of the whole path over a batch of 30 s synthetic chunks on
+each GPU: log-mel -> large-v3 encoder -> cross K/V + prompt prefill -> greedy
+decode of --new-tokens tokens per chunk under the timestamp-pair logit rules,
+driven by the continuous-batching scheduler.  Metric: audio seconds per wall
+second (RTFx), whole job over all ranks.
+
+  value : audio already resident in HBM when the timed region starts
+  e2e   : the same through the public API with pinned HOST audio (H2D inside)
+  roofline : the decode cross-attention kernel (the dominant byte mover),
+             timed with CUDA events inside the engine on one extra step
+  cpu_baseline : the CPU oracle port on a bounded sample, rank 0, N=1 only
+
+``--impl reference`` times the reference's CPU implementation of the path
+(the oracle port; the reference itself is pure Python and is not present on
+the GPU box) on the host cores, one bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+METRIC = "audio-sec/sec (RTFx)"
+UNIT = "audio-s/s"
+PROMPT = [50258, 50259, 50360]
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while running."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.rows, self.stop_flag = index, [], threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                parts = [x.strip() for x in out.stdout.strip().split(",")]
+                if len(parts) >= 6:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def summary(self) -> dict:
+        self.stop_flag.set()
+        self.join(timeout=6)
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = sorted(float(r[0]) for r in self.rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_sample(sd, dims, n_decode: int, new_tokens: int):
+    """One bounded sample of the CPU port: 1 clip through log-mel + encoder +
+    prefill + n_decode decode steps; returns (seconds for a full chunk by linear
+    extrapolation of the decode steps, description)."""
+    from oracle import oracle
+    from whisperdrz_b200 import synth
+    a = torch.from_numpy(synth.clip(1))
+    t0 = time.perf_counter()
+    mel = oracle.window_mel(oracle.log_mel(a))[None]
+    xa = oracle.encoder(sd, mel, dims.n_audio_layer, dims.n_audio_head)
+    dec = oracle.SlotDecoder(sd, dims.n_text_layer, dims.n_text_head, 1, dims.n_text_ctx)
+    logits = dec.prefill(torch.tensor([PROMPT]), xa, [0])[:, -1]
+    t1 = time.perf_counter()
+    for _ in range(n_decode):
+        nxt = logits.argmax(-1)
+        logits = dec.forward(nxt[:, None], [0])[:, 0]
+    t2 = time.perf_counter()
+    full = (t1 - t0) + (t2 - t1) / n_decode * new_tokens
+    return full, f"1 clip: log-mel + encoder + prefill + {n_decode} of {new_tokens} decode steps, decode extrapolated"
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from whisperdrz_b200.dims import ModelDimensions
+    from whisperdrz_b200.weights import init_state_dict
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    dims = ModelDimensions.from_name(args.model)
+    sd = init_state_dict(dims, 0)
+    times = []
+    for i in range(args.warmup + args.steps):
+        with torch.inference_mode():
+            full, sample = cpu_sample(sd, dims, args.cpu_decode_steps, args.new_tokens)
+        if i >= args.warmup:
+            times.append(full)
+    per_chunk = float(np.mean(times))
+    v = 30.0 / per_chunk
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_chunk * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args),
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args) -> dict:
+    return {"workload": f"batched 30 s chunks end to end (log-mel + {args.model} encoder + prefill + "
+                        f"{args.new_tokens}-token greedy decode with timestamp-pair rules), random-init weights",
+            "chunks_per_gpu_per_step": args.clips, "new_tokens": args.new_tokens, "prompt_len": len(PROMPT),
+            "parallelism": f"dp{args.gpus} (independent chunks, no collective on the path)",
+            "l2": "working set per decode step (cross K/V of all slots) is far larger than the 126 MB L2"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--model", default="large-v3")
+    ap.add_argument("--clips", type=int, default=32, help="30 s chunks per GPU per step")
+    ap.add_argument("--new-tokens", type=int, default=224)
+    ap.add_argument("--cpu-decode-steps", type=int, default=16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch.distributed as dist
+    from whisperdrz_b200 import synth
+    from whisperdrz_b200.dims import ModelDimensions
+    from whisperdrz_b200.engine import Engine
+    from whisperdrz_b200.rules import timestamp_tables
+    from whisperdrz_b200.transcriber import Transcriber
+    from whisperdrz_b200.weights import init_state_dict
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dims = ModelDimensions.from_name(args.model)
+    sd = init_state_dict(dims, 0)
+    eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(16, args.clips),
+                 tables=timestamp_tables(dims.n_vocab))
+    audio_host = torch.from_numpy(synth.clips([1000 * rank + i + 1 for i in range(args.clips)])).pin_memory()
+    audio_dev = audio_host.to(dev)
+
+    def one_step(src):
+        tr = Transcriber(eng, max_new_tokens=args.new_tokens)
+        for i in range(args.clips):
+            tr.pending_chunks.append({"audio": src[i], "id": f"chunk_{i}", "duration": 30.0, "offset": 0.0})
+        out = []
+        while tr.pending_chunks or any(s.status != "ready" for s in tr.states):
+            r = tr._run_batched_inference()
+            if r:
+                out.extend(r)
+        return tr, out
+
+    def timed(src, steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = eng.launch_count()
+        a.record()
+        n_tok = 0
+        dsteps = 0
+        for _ in range(steps):
+            tr, out = one_step(src)
+            n_tok += sum(len(r["tokens"]) for r in out)
+            dsteps += tr.steps
+        b.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.barrier()
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), n_tok, dsteps, eng.launch_count() - l0
+
+    for _ in range(args.warmup):
+        one_step(audio_dev)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, n_tok, dsteps, launches = timed(audio_dev, args.steps)
+    clocks = sampler.summary()
+    ms_e2e, n_tok_e, dsteps_e, _ = timed(audio_host, args.steps)
+
+    audio_s = 30.0 * args.clips * args.steps * world
+    value = audio_s / (ms / 1e3)
+    e2e = audio_s / (ms_e2e / 1e3)
+    rule_bytes = 128 * n_tok_e // max(args.steps, 1)
+    h2d = args.clips * 480000 * 4 + rule_bytes + 8 * n_tok_e // max(args.steps, 1)
+    d2h = 4 * n_tok_e // max(args.steps, 1)
+
+    # roofline of the dominant kernel, from one extra profiled step
+    eng.profile(True)
+    one_step(audio_dev)
+    prof = eng.profile_read()
+    eng.profile(False)
+    peak, peak_kind = peaks()
+    ca = prof["cross_attn"]
+    per_launch_ms = ca["ms"] / max(ca["launches"], 1)
+    per_launch_bytes = ca["work"] / max(ca["launches"], 1)
+    achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms > 0 else 0.0
+    shares = {k: round(v["ms"], 3) for k, v in prof.items()}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args),
+                "clocks": clocks,
+                "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+                "gpu_launches": int(launches),
+                "decode_tokens_per_s": n_tok * world / (ms / 1e3),
+                "roofline": {"kernel": "attn_dec_kernel (decode cross-attention)", "bound": "hbm",
+                             "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                             "frac": achieved / peak, "traffic": None,
+                             "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms},
+                "kernel_ms_one_step": shares}
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            with torch.inference_mode():
+                full, sample = cpu_sample(sd, dims, args.cpu_decode_steps, args.new_tokens)
+            line["cpu_baseline"] = {"value": 30.0 / full, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -104,6 +104,23 @@ const char* wdz_version(void);
  * Synchronises the stream. */
 int wdz_device_status(wdz_engine* e, wdz_stream s);
 
+/* ---- measurement (no counterpart in the reference, which ships no profiling) ---- */
+#define WDZ_PROF_CROSS_ATTN 0 /* decode cross-attention kernel; work = K/V bytes read */
+#define WDZ_PROF_SELF_ATTN 1  /* decode self-attention kernel; work not tracked (0) */
+#define WDZ_PROF_DEC_GEMM 2   /* decode-shaped products; work = weight bytes */
+#define WDZ_PROF_ENC_GEMM 3   /* encoder / conv / cross-KV products; work = flops */
+#define WDZ_PROF_ENC_ATTN 4   /* encoder attention; work = flops */
+#define WDZ_PROF_LM_HEAD 5    /* tied LM head; work = weight bytes */
+#define WDZ_PROF_LOGMEL 6     /* the three log-mel kernels together */
+/* Kernels enqueued by this engine since it was created. */
+int wdz_launch_count(const wdz_engine* e, int64_t* out);
+/* enable != 0: start recording a CUDA-event pair around every launch of the
+ * kinds above (and forget earlier records); 0: stop.  Recording costs a few
+ * microseconds per launch, so headline timings are taken with it off. */
+int wdz_profile(wdz_engine* e, int enable);
+/* Synchronises the device, then sums the recorded launches of one kind. */
+int wdz_profile_read(wdz_engine* e, int kind, double* total_ms, int64_t* launches, double* work);
+
 /* ---- front end: LogMelSpectrogram.forward (audio.py:108-156) ----------- */
 /* audio_dev f32 [B, audio_stride]; n_samples_dev int32 [B] (>= 400 each, the
  * reflect padding needs it); frame_offset_dev int32 [B] or NULL: first frame

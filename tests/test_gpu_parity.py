@@ -35,14 +35,14 @@ def _engine(name, dtype, seed=0, **kw):
 
 @pytest.fixture(scope="module")
 def small_f32():
-    e, dims, sd = _engine("test-small", torch.float32, n_slots=6, max_clips=2)
+    e, dims, sd = _engine("test-small", torch.float32, n_slots=6, max_clips=3)
     yield e, dims, sd
     e.close()
 
 
 @pytest.fixture(scope="module")
 def small_bf16():
-    e, dims, sd = _engine("test-small", torch.bfloat16, n_slots=6, max_clips=2)
+    e, dims, sd = _engine("test-small", torch.bfloat16, n_slots=6, max_clips=3)
     yield e, dims, sd
     e.close()
 
@@ -235,7 +235,7 @@ def test_capacity_and_argument_errors(small_f32):
     from whisperdrz_b200.capi import WdzError
     e, dims, _ = small_f32
     with pytest.raises(WdzError):
-        e.encode(torch.zeros(3, dims.n_mels, 3000))          # > max_clips
+        e.encode(torch.zeros(4, dims.n_mels, 3000))          # > max_clips
     with pytest.raises(WdzError):
         e.decode_step([1] * 100, [0] * 100)                  # > max_rows
     with pytest.raises(ValueError):

@@ -15,6 +15,8 @@ WDZ_F32, WDZ_BF16 = 0, 1
 FLAG_NO_TENSOR_CORE = 1
 MODE_OR, MODE_ALL_EXCEPT_TABLE, MODE_ALL_EXCEPT_RANGE, MODE_ALL = 0, 1, 2, 3
 MAX_TABLES = 32
+PROF_KINDS = {"cross_attn": 0, "self_attn": 1, "dec_gemm": 2, "enc_gemm": 3, "enc_attn": 4, "lm_head": 5,
+              "logmel": 6}
 
 
 class WdzError(RuntimeError):
@@ -52,6 +54,9 @@ SYMBOLS = {
     "wdz_last_error": (C.c_char_p, [P]),
     "wdz_version": (C.c_char_p, []),
     "wdz_device_status": (I, [P, P]),
+    "wdz_launch_count": (I, [P, C.POINTER(I64)]),
+    "wdz_profile": (I, [P, I]),
+    "wdz_profile_read": (I, [P, I, C.POINTER(C.c_double), C.POINTER(I64), C.POINTER(C.c_double)]),
     "wdz_logmel": (I, [P, P, I64, P, P, I, P, P]),
     "wdz_encode": (I, [P, P, I, P, P]),
     "wdz_cross_kv": (I, [P, P, P, I, P]),

@@ -72,6 +72,27 @@ struct wdz_engine {
   int64_t part_entries = 0;
   int max_emit = 0;
   int last_emit = 0;  // logit rows held from the last forward
+  long long launches = 0;  // kernels enqueued since creation
+
+  // optional per-kernel timing (wdz_profile): event pairs around selected launches
+  struct Span { cudaEvent_t a, b; int kind; double work; };
+  bool profiling = false;
+  std::vector<Span> spans;
+  size_t spans_used = 0;
+  int span_begin(int kind, double work, cudaStream_t s) {
+    if (!profiling) return -1;
+    if (spans_used == spans.size()) {
+      if (spans.size() >= 65536) return -1;
+      Span sp{};
+      if (cudaEventCreate(&sp.a) != cudaSuccess || cudaEventCreate(&sp.b) != cudaSuccess) { cudaGetLastError(); return -1; }
+      spans.push_back(sp);
+    }
+    Span& sp = spans[spans_used];
+    sp.kind = kind; sp.work = work;
+    cudaEventRecord(sp.a, s);
+    return (int)spans_used++;
+  }
+  void span_end(int id, cudaStream_t s) { if (id >= 0) cudaEventRecord(spans[id].b, s); }
 
   int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -88,6 +109,7 @@ namespace {
 
 #define WDZ_LAUNCH_CHECK(e, what)                                                   \
   do {                                                                              \
+    (e)->launches += 1;                                                             \
     cudaError_t _c = cudaGetLastError();                                            \
     if (_c != cudaSuccess) return (e)->fail(WDZ_ECUDA, "%s: %s", what, cudaGetErrorString(_c)); \
   } while (0)
@@ -166,13 +188,14 @@ GemmParams dense_params(const void* A, int64_t lda, const void* W, const void* b
 // bf16 case when it is compiled in and not disabled.
 template <typename T>
 int enc_gemm(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s) {
+  const int sp = e->span_begin(WDZ_PROF_ENC_GEMM, 2.0 * p.M * p.N * p.K, s);
+  int rc = 1;
 #ifdef WDZ_WITH_TC
-  if (sizeof(T) == 2 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) {
-    int rc = gemm_tc_launch(e, epi, p, s);
-    if (rc != 1) return rc;  // 1 = shape not supported, fall through
-  }
+  if (sizeof(T) == 2 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) rc = gemm_tc_launch(e, epi, p, s);
 #endif
-  return launch_gemm_tile<T, T, T>(e, epi, p, s);
+  if (rc == 1) rc = launch_gemm_tile<T, T, T>(e, epi, p, s);  // 1 = shape not taken by the tensor-core kernel
+  e->span_end(sp, s);
+  return rc;
 }
 
 template <typename T, int EPI>
@@ -194,17 +217,23 @@ int launch_gemv(wdz_engine* e, const GemvParams& p, cudaStream_t s) {
 template <typename T>
 int dec_gemm(wdz_engine* e, int epi, const float* x, int64_t ldx, const void* W, const void* bias,
              float* y, int64_t ldy, int M, int N, int K, const int* row_idx, cudaStream_t s) {
+  const int sp = e->span_begin(W == e->tok_emb ? WDZ_PROF_LM_HEAD : WDZ_PROF_DEC_GEMM,
+                               (double)N * K * sizeof(T), s);
+  int rc;
   if (M <= 64 || row_idx) {
     GemvParams p{x, W, bias, y, M, N, K, ldx, ldy, row_idx};
     switch (epi) {
-      case EPI_STORE: return launch_gemv<T, EPI_STORE>(e, p, s);
-      case EPI_GELU: return launch_gemv<T, EPI_GELU>(e, p, s);
-      case EPI_RESID: return launch_gemv<T, EPI_RESID>(e, p, s);
-      default: return e->fail(WDZ_EINVAL, "bad decode epilogue %d", epi);
+      case EPI_STORE: rc = launch_gemv<T, EPI_STORE>(e, p, s); break;
+      case EPI_GELU: rc = launch_gemv<T, EPI_GELU>(e, p, s); break;
+      case EPI_RESID: rc = launch_gemv<T, EPI_RESID>(e, p, s); break;
+      default: rc = e->fail(WDZ_EINVAL, "bad decode epilogue %d", epi);
     }
+  } else {
+    GemmParams p = dense_params(x, ldx, W, bias, y, ldy, M, N, K);
+    rc = launch_gemm_tile<float, T, float>(e, epi, p, s);
   }
-  GemmParams p = dense_params(x, ldx, W, bias, y, ldy, M, N, K);
-  return launch_gemm_tile<float, T, float>(e, epi, p, s);
+  e->span_end(sp, s);
+  return rc;
 }
 
 template <typename TP, typename TO>
@@ -249,8 +278,12 @@ int encode_impl(wdz_engine* e, const float* mel, int B, void* xa_out, cudaStream
     const LayerW& w = e->enc[l];
     if ((rc = launch_ln<T, T>(e, e->x, d, nullptr, w.ln1_w, w.ln1_b, (T*)e->xn, d, M, d, s))) return rc;
     if ((rc = enc_gemm<T>(e, EPI_STORE, dense_params(e->xn, d, w.qkv_w, w.qkv_b, e->qkv, 3 * d, M, 3 * d, d), s))) return rc;
-    attn_enc_simt_kernel<T><<<dim3((Ta + 63) / 64, H, B), 256, attn_enc_simt_smem(), s>>>(
-        (const T*)e->qkv, (T*)e->ao, Ta, d);
+    {
+      const int sp = e->span_begin(WDZ_PROF_ENC_ATTN, 4.0 * B * H * (double)Ta * Ta * HD, s);
+      attn_enc_simt_kernel<T><<<dim3((Ta + 63) / 64, H, B), 256, attn_enc_simt_smem(), s>>>(
+          (const T*)e->qkv, (T*)e->ao, Ta, d);
+      e->span_end(sp, s);
+    }
     WDZ_LAUNCH_CHECK(e, "attn_enc");
     if ((rc = enc_gemm<T>(e, EPI_RESID, dense_params(e->ao, d, w.out_w, w.out_b, e->x, d, M, d, d), s))) return rc;
     if ((rc = launch_ln<T, T>(e, e->x, d, nullptr, w.ln2_w, w.ln2_b, (T*)e->xn, d, M, d, s))) return rc;
@@ -288,8 +321,12 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
   if ((int64_t)rows * splits > e->part_entries)
     return e->fail(WDZ_ECAPACITY, "attention partials: %d rows x %d splits exceed the workspace", rows, splits);
   p.max_splits = splits;
+  const int sp = e->span_begin(cross ? WDZ_PROF_CROSS_ATTN : WDZ_PROF_SELF_ATTN,
+                               cross ? 2.0 * rows * max_len * p.d * sizeof(T) : 0.0, s);
   attn_dec_kernel<T><<<dim3(splits, rows), H * 32, 0, s>>>(p);
+  e->span_end(sp, s);
   attn_dec_combine_kernel<<<rows, H * 32, 0, s>>>(p);
+  e->launches += 1;
   WDZ_LAUNCH_CHECK(e, "attn_dec");
   return WDZ_OK;
 }
@@ -393,6 +430,7 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
 }
 
 int wdz_engine_destroy(wdz_engine* e) {
+  if (e) for (auto& sp : e->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
   delete e;
   return WDZ_OK;
 }
@@ -529,6 +567,36 @@ int wdz_device_status(wdz_engine* e, wdz_stream s) {
   return WDZ_OK;
 }
 
+int wdz_launch_count(const wdz_engine* e, int64_t* out) {
+  if (!e || !out) return WDZ_EINVAL;
+  *out = e->launches;
+  return WDZ_OK;
+}
+
+int wdz_profile(wdz_engine* e, int enable) {
+  if (!e) return WDZ_EINVAL;
+  e->profiling = enable != 0;
+  if (enable) e->spans_used = 0;
+  return WDZ_OK;
+}
+
+int wdz_profile_read(wdz_engine* e, int kind, double* total_ms, int64_t* launches, double* work) {
+  if (!e || !total_ms || !launches || !work) return WDZ_EINVAL;
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "profile read: %s", cudaGetErrorString(ce));
+  }
+  *total_ms = 0.0; *launches = 0; *work = 0.0;
+  for (size_t i = 0; i < e->spans_used; ++i) {
+    const wdz_engine::Span& sp = e->spans[i];
+    if (sp.kind != kind) continue;
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, sp.a, sp.b) != cudaSuccess) { cudaGetLastError(); continue; }
+    *total_ms += ms; *launches += 1; *work += sp.work;
+  }
+  return WDZ_OK;
+}
+
 int wdz_logmel(wdz_engine* e, const float* audio_dev, int64_t audio_stride, const int32_t* n_samples_dev,
                const int32_t* frame_offset_dev, int B, float* mel_out_dev, wdz_stream s) {
   int rc = check_ready(e);
@@ -537,11 +605,14 @@ int wdz_logmel(wdz_engine* e, const float* audio_dev, int64_t audio_stride, cons
   if (B == 0) return WDZ_OK;
   if (B > e->cfg.max_clips) return e->fail(WDZ_ECAPACITY, "wdz_logmel: %d clips > max_clips %d", B, e->cfg.max_clips);
   cudaStream_t st = (cudaStream_t)s;
+  const int sp = e->span_begin(WDZ_PROF_LOGMEL, 0.0, st);
   logmel_init_max_kernel<<<(B + 255) / 256, 256, 0, st>>>(e->clipmax, B);
   logmel_raw_kernel<<<dim3((MEL_MAX_FRAMES + MEL_FT - 1) / MEL_FT, B), 256, logmel_smem_bytes(), st>>>(
       audio_dev, audio_stride, n_samples_dev, e->mel, e->cfg.n_mels, e->mel_raw, e->clipmax);
   logmel_finalize_kernel<<<dim3((MEL_MAX_FRAMES + 255) / 256, e->cfg.n_mels, B), 256, 0, st>>>(
       e->mel_raw, e->clipmax, n_samples_dev, frame_offset_dev, e->cfg.n_mels, mel_out_dev);
+  e->span_end(sp, st);
+  e->launches += 2;
   WDZ_LAUNCH_CHECK(e, "logmel");
   return WDZ_OK;
 }

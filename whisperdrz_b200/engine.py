@@ -191,6 +191,24 @@ class Engine:
         """Raises if a kernel flagged an error (NaN logits row, exhausted wait)."""
         self._check(self.lib.wdz_device_status(self.h, self._stream()))
 
+    # ----------------------------------------------------------- measurement
+    def launch_count(self) -> int:
+        out = C.c_int64()
+        self._check(self.lib.wdz_launch_count(self.h, C.byref(out)))
+        return out.value
+
+    def profile(self, enable: bool) -> None:
+        self._check(self.lib.wdz_profile(self.h, int(enable)))
+
+    def profile_read(self) -> dict:
+        """{kind: {"ms", "launches", "work"}} for the launches recorded since profile(True)."""
+        res = {}
+        for name, kind in capi.PROF_KINDS.items():
+            ms, n, work = C.c_double(), C.c_int64(), C.c_double()
+            self._check(self.lib.wdz_profile_read(self.h, kind, C.byref(ms), C.byref(n), C.byref(work)))
+            res[name] = {"ms": ms.value, "launches": n.value, "work": work.value}
+        return res
+
     # ------------------------------------------------------------- front end
     def logmel(self, audio: torch.Tensor, n_samples=None, frame_offset=None) -> torch.Tensor:
         """audio f32 [B, N] (device) -> mel f32 [B, n_mels, 3000]."""

@@ -1,0 +1,225 @@
+"""Continuous-batching scheduler and chunk-and-stitch front of the engine.
+
+Mirrors the control flow of the reference ``Transcriber``
+(src/whisperdrz/transcriber.py): ``transcribe(audio)`` splits audio into 30 s
+chunks (:780-793), chunks wait in ``pending_chunks``, free slots are filled
+and prefilled (:1555-1567, ``_init_slot`` :903-974, ``_prefill_slots``
+:1042-1145), every loop iteration decodes one token for all started slots
+(:1666-1744), finished slots are emitted and refilled at once (:1790-1815),
+results are ordered by chunk id and joined (:803-810); ``__call__`` / ``flush``
+give the pipeline form (:833-870, :1831-1844).
+
+What changes is the device side of each step: one rule-descriptor upload, one
+fused engine call (forward over all active rows, logit rules, argmax) and one
+4-byte-per-row download replace the reference's ~30 mask kernels, bucketed
+graph replay and six small copies.  Rules are the token-level subset of
+``whisperdrz_b200.rules``; text-level rules, DTW word timing and the text
+clean-up chain of the reference are not part of this path.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .dims import SAMPLE_RATE, TOK_EOT, TOK_LANG_EN, TOK_SOT, TOK_TRANSCRIBE
+from .rules import RowState, segments as token_segments
+
+
+@dataclass
+class TranscribeResults:
+    """Same fields as the reference's TranscribeResults (transcriber.py:222-226)."""
+    text: str
+    raw_chunks: list | None = None
+    segments: list | None = None
+
+
+@dataclass
+class Slot:
+    index: int
+    status: str = "ready"            # ready -> started -> finished -> ready (transcriber.py:505-509)
+    chunk: dict | None = None
+    row: RowState | None = None
+    last_token: int = 0
+    stop_reason: str = ""
+
+
+def rules_to_array(rules: list[dict]) -> np.ndarray:
+    """Rule dicts -> int32 [n, 32] in ``wdz_rule_desc`` layout."""
+    a = np.zeros((len(rules), 32), dtype=np.int32)
+    a[:, 0] = -1
+    for i, r in enumerate(rules):
+        if "forced_id" in r:
+            a[i, 0] = r["forced_id"]
+            continue
+        a[i, 1] = r.get("mode", 0)
+        a[i, 2] = r.get("arg0", 0)
+        a[i, 3] = r.get("arg1", 0)
+        a[i, 4] = np.int64(r.get("table_bits", 0)).astype(np.int32)
+        a[i, 5] = r.get("prefix_begin", 0)
+        a[i, 6] = r.get("prefix_end", 0)
+        for base, cap, key in ((7, 8, "set_ids"), (16, 4, "clear_ids"), (21, 10, "pen_ids")):
+            ids = list(dict.fromkeys(r.get(key, ())))[:cap]
+            a[i, base] = len(ids)
+            a[i, base + 1: base + 1 + len(ids)] = ids
+    return a
+
+
+class Transcriber:
+    def __init__(self, engine, BS: int | None = None, max_audio_length: float = 30.0,
+                 max_new_tokens: int = 224, lang: str | None = "en", use_rules: bool = True,
+                 text_decoder=None):
+        """engine: ``whisperdrz_b200.engine.Engine`` (or an object with the same
+        methods).  BS: concurrent slots, at most the engine's.  max_new_tokens:
+        generated tokens per 30 s window before EOT is forced.  text_decoder:
+        optional ``list[int] -> str`` (the tokenizer is not part of this path)."""
+        self.engine = engine
+        self.BS = BS or engine.n_slots
+        if self.BS > engine.n_slots:
+            raise ValueError("BS exceeds the engine's slot count")
+        self.max_audio_length = max_audio_length
+        self.max_new_tokens = max_new_tokens
+        self.use_rules = use_rules
+        self.text_decoder = text_decoder
+        self.init_tokens = [TOK_SOT, TOK_LANG_EN, TOK_TRANSCRIBE] if lang else [TOK_SOT]
+        if len(self.init_tokens) + max_new_tokens > engine.max_tokens:
+            raise ValueError("prompt + max_new_tokens exceed the KV cache length")
+        self.states = [Slot(i) for i in range(self.BS)]
+        self.pending_chunks: list[dict] = []
+        self.seconds_processed = 0.0
+        self.steps = 0
+        self.launch_rows = 0
+        self._pin_rules = None
+        self._pin_tok = None
+
+    # ------------------------------------------------------------------ public
+    def transcribe(self, audio) -> TranscribeResults:
+        """audio: 1-D float array/tensor at 16 kHz (host or device)."""
+        if isinstance(audio, np.ndarray):
+            audio = torch.from_numpy(audio)
+        audio = audio.squeeze()
+        chunk_len = int(self.max_audio_length * SAMPLE_RATE)
+        for i, start in enumerate(range(0, len(audio), chunk_len)):
+            end = min(start + chunk_len, len(audio))
+            self.pending_chunks.append({"audio": audio[start:end], "id": f"chunk_{i}",
+                                        "duration": (end - start) / SAMPLE_RATE, "offset": start / SAMPLE_RATE})
+        results = []
+        while self.pending_chunks or any(s.status != "ready" for s in self.states):
+            r = self._run_batched_inference()
+            if r:
+                results.extend(r)
+        return self.stitch(results)
+
+    def stitch(self, results: list[dict]) -> TranscribeResults:
+        results.sort(key=lambda r: int(str(r.get("id", "chunk_0")).split("_")[-1]))
+        segs = [s for r in results for s in r["segments"]]
+        text = "\n".join(r.get("prediction", "") for r in results) if self.text_decoder else ""
+        return TranscribeResults(text=text, raw_chunks=results, segments=segs)
+
+    def __call__(self, chunk):
+        if isinstance(chunk, list):
+            self.pending_chunks.extend(c for c in chunk if isinstance(c, dict))
+        elif isinstance(chunk, dict):
+            self.pending_chunks.append(chunk)
+        ready = sum(1 for s in self.states if s.status == "ready")
+        if self.pending_chunks and len(self.pending_chunks) >= ready:
+            return self._run_batched_inference()
+        return None
+
+    def flush(self):
+        while self.pending_chunks or any(s.status != "ready" for s in self.states):
+            r = self._run_batched_inference()
+            if r:
+                yield from r
+
+    # ---------------------------------------------------------------- internals
+    def _init_slot(self, slot: Slot, chunk: dict) -> None:
+        slot.chunk = chunk
+        slot.status = "started"
+        slot.row = RowState(max_new=self.max_new_tokens)
+        slot.stop_reason = ""
+
+    def _prefill_slots(self, slots: list[Slot]) -> None:
+        """Log-mel + encoder + cross K/V + prompt for new slots, then their first token."""
+        eng = self.engine
+        dev = eng.device
+        for g0 in range(0, len(slots), eng.max_clips):
+            grp = slots[g0: g0 + eng.max_clips]
+            n = [min(len(s.chunk["audio"]), 480000) for s in grp]
+            first = grp[0].chunk["audio"]
+            if isinstance(first, torch.Tensor) and first.is_cuda:
+                buf = torch.zeros(len(grp), 480000, dtype=torch.float32, device=dev)
+                for i, s in enumerate(grp):
+                    buf[i, : n[i]] = s.chunk["audio"][: n[i]]
+            else:
+                host = torch.zeros(len(grp), 480000, dtype=torch.float32).pin_memory()
+                for i, s in enumerate(grp):
+                    host[i, : n[i]] = torch.as_tensor(s.chunk["audio"][: n[i]], dtype=torch.float32)
+                buf = host.to(dev, non_blocking=True)
+            mel = eng.logmel(buf, n_samples=n)
+            xa = eng.encode(mel)
+            ids = [s.index for s in grp]
+            logits = eng.prefill(xa, ids, [self.init_tokens] * len(grp))
+            rules = [s.row.rule() for s in grp] if self.use_rules else None
+            first_tok = eng.rules_argmax(logits, None if rules is None else self._rules_dev(rules)).tolist()
+            for s, t in zip(grp, first_tok):
+                self._accept(s, int(t))
+
+    def _rules_dev(self, rules: list[dict]) -> torch.Tensor:
+        a = torch.from_numpy(rules_to_array(rules))
+        return a.to(self.engine.device, non_blocking=False)
+
+    def _accept(self, slot: Slot, tok: int) -> None:
+        slot.row.update(tok)
+        slot.last_token = tok
+        if slot.row.done:
+            slot.status = "finished"
+            slot.stop_reason = "eot" if tok == TOK_EOT else "nan_logits"
+            if slot.row.n_new >= slot.row.max_new:
+                slot.stop_reason = "max_tokens"
+
+    def _finish(self, slot: Slot) -> dict:
+        c = slot.chunk
+        toks = [t for t in slot.row.tokens if t != TOK_EOT]
+        res = {k: v for k, v in c.items() if k not in ("audio", "mel")}
+        res.update(id=c["id"], tokens=toks, stop_reason=slot.stop_reason,
+                   segments=token_segments(toks, c.get("offset", 0.0)))
+        if self.text_decoder:
+            res["prediction"] = self.text_decoder(toks)
+        self.seconds_processed += c.get("duration", 0.0)
+        slot.status, slot.chunk, slot.row = "ready", None, None
+        return res
+
+    @torch.inference_mode()
+    def _run_batched_inference(self):
+        eng = self.engine
+        done: list[dict] = []
+        while True:
+            new = []
+            for s in self.states:
+                if s.status == "ready" and self.pending_chunks:
+                    self._init_slot(s, self.pending_chunks.pop(0))
+                    new.append(s)
+            if new:
+                self._prefill_slots(new)
+            for s in self.states:
+                if s.status == "finished":
+                    done.append(self._finish(s))
+            active = [s for s in self.states if s.status == "started"]
+            if not active:
+                if self.pending_chunks:
+                    continue
+                break
+            rules = self._rules_dev([s.row.rule() for s in active]) if self.use_rules else None
+            nxt = eng.decode_step([s.last_token for s in active], [s.index for s in active], rules=rules)
+            self.steps += 1
+            self.launch_rows += len(active)
+            for s, t in zip(active, nxt.tolist()):
+                self._accept(s, int(t))
+            finished = [s for s in self.states if s.status == "finished"]
+            for s in finished:
+                done.append(self._finish(s))
+            if finished and not self.pending_chunks and not any(s.status == "started" for s in self.states):
+                break
+        return done or None
