@@ -87,7 +87,7 @@ int wdz_engine_destroy(wdz_engine* e);
 int wdz_workspace_bytes(const wdz_engine* e, size_t* out_bytes);
 int wdz_set_workspace(wdz_engine* e, void* dev, size_t bytes);
 /* Lend the engine one tensor (dtype = cfg.dtype unless noted).  Names are
- * listed in whisperdrz_b200/engine.py (ENGINE_TENSORS): the reference's
+ * those produced by pack_weights in whisperdrz_b200/engine.py: the reference's
  * state_dict tensors (model.py:258-261,387-394,449-461,493-529), with q/k/v
  * stacked per attention and the conv kernels tap-major, plus
  *   cache.self_k / cache.self_v   [n_text_layer, n_slots, max_tokens, n_text_state]
@@ -133,6 +133,13 @@ int wdz_logmel(wdz_engine* e, const float* audio_dev, int64_t audio_stride,
 /* ---- encoder: AudioEncoder.forward (model.py:462-475) ------------------ */
 /* mel_dev f32 [B, n_mels, 3000] -> xa_out_dev [B, n_audio_ctx, n_audio_state] in cfg.dtype */
 int wdz_encode(wdz_engine* e, const float* mel_dev, int B, void* xa_out_dev, wdz_stream s);
+
+/* One nn.Linear (+ exact GELU when gelu != 0) in cfg.dtype, as the encoder
+ * runs it (model.py:258-261, 387-393): y[M,N] = act(x[M,K] w[N,K]^T + bias).
+ * bias_dev may be NULL.  cuda_cores_only != 0 keeps a bf16 product off the
+ * tcgen05 kernel (for A/B checks). */
+int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev, const void* bias_dev, int N,
+               int gelu, void* y_dev, int cuda_cores_only, wdz_stream s);
 
 /* ---- decoder ----------------------------------------------------------- */
 /* Cross K/V of all layers for B windows into their slots

@@ -240,3 +240,26 @@ def test_capacity_and_argument_errors(small_f32):
         e.decode_step([1] * 100, [0] * 100)                  # > max_rows
     with pytest.raises(ValueError):
         e.logmel(torch.zeros(1, 300))                        # too short to reflect-pad
+
+
+# ------------------------------------------------------------------- tcgen05 GEMM
+@pytest.mark.parametrize("M,N,K,gelu", [(128, 256, 64, False), (300, 512, 256, True), (3000, 1280, 384, True),
+                                        (1500, 3840, 1280, False), (777, 1280, 5120, False)])
+def test_tensor_core_linear_matches_fp32_reference(small_bf16, M, N, K, gelu):
+    """tcgen05 GEMM against a plain fp32 product of the same bf16-rounded
+    operands; tolerance = bf16 output rounding (2^-8 relative) plus fp32
+    accumulation-order noise."""
+    e, _, _ = small_bf16
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
+    b = (torch.randn(N, generator=g) * 0.1).bfloat16()
+    ref = x.float() @ w.float().T + b.float()
+    if gelu:
+        ref = torch.nn.functional.gelu(ref)
+    got = e.linear(x, w, b, gelu=gelu).float().cpu()
+    e.device_status()
+    err = (got - ref).abs().max() / ref.abs().max()
+    assert err < 6e-3, err
+    got_cc = e.linear(x, w, b, gelu=gelu, cuda_cores_only=True).float().cpu()
+    assert (got - got_cc).abs().max() / ref.abs().max() < 6e-3

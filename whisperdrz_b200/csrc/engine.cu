@@ -26,6 +26,12 @@
 
 using namespace wdz;
 
+#ifdef WDZ_WITH_TC
+struct wdz_engine;
+static int gemm_tc_init(wdz_engine* e);
+static int gemm_tc_launch(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s);
+#endif
+
 namespace {
 
 struct Bound { const void* ptr; int64_t numel; };
@@ -336,7 +342,7 @@ template <typename T>
 int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const int* positions, int n,
                       const int* emit_rows, int n_emit, cudaStream_t s) {
   const wdz_config& c = e->cfg;
-  const int d = c.n_text_state, H = c.n_text_head;
+  const int d = c.n_text_state;
   int rc;
   embed_kernel<T><<<n, 256, 0, s>>>(tokens, positions, (const T*)e->tok_emb, (const T*)e->dec_pos, e->dx, n, d,
                                      c.n_vocab, c.n_text_ctx);
@@ -396,6 +402,59 @@ int rules_launch(wdz_engine* e, const float* logits, const int* row_idx, const w
 }
 
 }  // namespace
+
+#ifdef WDZ_WITH_TC
+// Tensor-core path: returns WDZ_OK when launched, 1 when the shape is left to
+// the CUDA-core kernel, a negative code on failure.
+static int gemm_tc_init(wdz_engine* e) {
+  if (!tc::encode_fn()) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    }
+    tc::encode_fn() = (tc::EncodeTiledFn)fn;
+  }
+  if (cudaFuncSetAttribute(tc::gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES) !=
+      cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "gemm_tc smem attribute: %s", cudaGetErrorString(ce));
+  }
+  return WDZ_OK;
+}
+
+static int gemm_tc_launch(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s) {
+  if (p.N % tc::BN || p.K % tc::BK || p.M < 1) return 1;
+  if (((uintptr_t)p.A | (uintptr_t)p.W) & 15) return 1;
+  if ((p.lda * 2) % 16 || (p.a_bstride * 2) % 16) return 1;
+  if (epi != EPI_CROSS_KV && ((uintptr_t)p.C & 15)) return 1;
+  if (epi != EPI_CROSS_KV && (p.ldc % 8 || p.c_bstride % 8)) return 1;
+  if (epi == EPI_CROSS_KV && p.d % 32) return 1;
+  tc::TcParams tp{};
+  tp.g = p;
+  tp.epi = epi;
+  tp.status = e->status;
+  const int rpb = p.a_rpb;
+  tp.batches = (p.M + rpb - 1) / rpb;
+  tp.tiles_m_per_batch = (rpb + tc::BM - 1) / tc::BM;
+  tp.tiles_n = p.N / tc::BN;
+  tp.total_tiles = tp.batches * tp.tiles_m_per_batch * tp.tiles_n;
+  tp.kblocks = p.K / tc::BK;
+  CUtensorMap ma, mw;
+  const uint64_t s1 = (uint64_t)p.lda * 2;
+  const uint64_t s2 = tp.batches > 1 ? (uint64_t)p.a_bstride * 2 : s1 * (uint64_t)rpb;
+  const uint64_t rows_last = tp.batches > 1 ? (uint64_t)rpb : (uint64_t)p.M;
+  if (!tc::make_map(&ma, p.A, (uint64_t)p.K, rows_last, (uint64_t)tp.batches, s1, s2, tc::BM, 3)) return 1;
+  if (!tc::make_map(&mw, p.W, (uint64_t)p.K, (uint64_t)p.N, 1, (uint64_t)p.K * 2, (uint64_t)p.K * 2 * p.N, tc::BN, 2))
+    return 1;
+  const int grid = tp.total_tiles < e->sm_count ? tp.total_tiles : e->sm_count;
+  tc::gemm_tc_kernel<<<grid, tc::THREADS, tc::SMEM_BYTES, s>>>(ma, mw, tp);
+  WDZ_LAUNCH_CHECK(e, "gemm_tc");
+  return WDZ_OK;
+}
+#endif
 
 // ---------------------------------------------------------------------------
 // C ABI
@@ -565,6 +624,22 @@ int wdz_device_status(wdz_engine* e, wdz_stream s) {
     return e->fail(h.code, "device reported status %d (detail %d)", h.code, h.detail);
   }
   return WDZ_OK;
+}
+
+int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev, const void* bias_dev, int N,
+               int gelu, void* y_dev, int cuda_cores_only, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!x_dev || !w_dev || !y_dev || M < 1 || N < 1 || K < 1) return e->fail(WDZ_EINVAL, "wdz_linear: bad argument");
+  GemmParams p = dense_params(x_dev, K, w_dev, bias_dev, y_dev, N, M, N, K);
+  const int epi = gelu ? EPI_GELU : EPI_STORE;
+  cudaStream_t st = (cudaStream_t)s;
+  if (e->cfg.dtype == WDZ_F32) return launch_gemm_tile<float, float, float>(e, epi, p, st);
+  const int saved = e->cfg.flags;
+  if (cuda_cores_only) e->cfg.flags |= WDZ_FLAG_NO_TENSOR_CORE;
+  rc = enc_gemm<bf16>(e, epi, p, st);
+  e->cfg.flags = saved;
+  return rc;
 }
 
 int wdz_launch_count(const wdz_engine* e, int64_t* out) {

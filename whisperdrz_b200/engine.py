@@ -237,6 +237,19 @@ class Engine:
         self._check(self.lib.wdz_encode(self.h, mel.data_ptr(), B, xa.data_ptr(), self._stream()))
         return xa
 
+    def linear(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gelu: bool = False,
+               cuda_cores_only: bool = False) -> torch.Tensor:
+        """act(x @ w.T + bias) in the engine dtype through the engine's GEMM kernels."""
+        x = x.to(device=self.device, dtype=self.dtype).contiguous()
+        w = w.to(device=self.device, dtype=self.dtype).contiguous()
+        b = None if bias is None else bias.to(device=self.device, dtype=self.dtype).contiguous()
+        M, K = x.shape
+        N = w.shape[0]
+        y = torch.empty(M, N, dtype=self.dtype, device=self.device)
+        self._check(self.lib.wdz_linear(self.h, x.data_ptr(), M, K, w.data_ptr(), None if b is None else b.data_ptr(),
+                                        N, int(gelu), y.data_ptr(), int(cuda_cores_only), self._stream()))
+        return y
+
     # --------------------------------------------------------------- decoder
     def cross_kv(self, xa: torch.Tensor, slots) -> None:
         xa = xa.to(self.dtype).contiguous()
