@@ -10,6 +10,7 @@
 //       element of the attended range is read exactly once per row, with
 //       16-byte loads that cover whole 128-byte head vectors.
 #pragma once
+#include "../../include/wdz.h"
 #include "common.cuh"
 
 namespace wdz {
@@ -131,17 +132,22 @@ struct AttnDecParams {
   const int* slots; const int* positions; int fixed_len;  // len = positions ? positions[r] + 1 : fixed_len
   int chunk, max_splits;
   float* part_o; float* part_ml;    // [rows, max_splits, H, 64] and [rows, max_splits, H, 2]
-  float* out; int64_t ldo;          // combine: out + r * ldo + h * 64
+  void* out; int64_t ldo;           // combine: out (TO) + r * ldo + h * 64
 };
 
-// Block = H warps (warp = head); grid = (splits, rows).
+// Block = a group of heads (warp = head); grid = (splits, rows, head groups).
+// The K/V loads of the next 2*KPI keys are issued before the current ones are
+// consumed, so every lane keeps eight 16-byte loads in flight.
 template <typename T>
-__global__ void attn_dec_kernel(AttnDecParams p) {
+__global__ void __launch_bounds__(256) attn_dec_kernel(AttnDecParams p) {
   constexpr int VEC = Vec<T>::N;   // elements per 16-byte piece
   constexpr int LPK = HD / VEC;    // lanes covering one key's head vector
-  constexpr int KPI = 32 / LPK;    // keys per warp iteration
+  constexpr int KPI = 32 / LPK;    // keys per warp load
+  constexpr int STEP = 2 * KPI;    // keys per loop iteration
   const int r = blockIdx.y, split = blockIdx.x;
-  const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, H = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int h = blockIdx.z * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int H = gridDim.z * (blockDim.x >> 5);
   const int slot = p.slots[r];
   if (slot < 0 || slot >= p.n_slots) return;
   int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
@@ -165,14 +171,19 @@ __global__ void attn_dec_kernel(AttnDecParams p) {
 #pragma unroll
   for (int e = 0; e < VEC; ++e) o[e] = 0.0f;
 
-  for (int t0 = start; t0 < end; t0 += 2 * KPI) {
+  float ka[VEC], kb[VEC], xa[VEC], xb[VEC];      // current keys / values
+  float nka[VEC], nkb[VEC], nxa[VEC], nxb[VEC];  // next iteration's
+  auto fetch = [&](int t0, float (&k0)[VEC], float (&k1)[VEC], float (&v0)[VEC], float (&v1)[VEC]) {
     const int ta = t0 + grp, tb = t0 + KPI + grp;
-    const bool va = ta < end, vb = tb < end;
-    float ka[VEC], kb[VEC], xa[VEC], xb[VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) ka[e] = kb[e] = xa[e] = xb[e] = 0.0f;
-    if (va) { load_vec_nc(K + (int64_t)ta * p.d, ka); load_vec_nc(V + (int64_t)ta * p.d, xa); }
-    if (vb) { load_vec_nc(K + (int64_t)tb * p.d, kb); load_vec_nc(V + (int64_t)tb * p.d, xb); }
+    for (int e = 0; e < VEC; ++e) k0[e] = k1[e] = v0[e] = v1[e] = 0.0f;
+    if (ta < end) { load_vec_nc(K + (int64_t)ta * p.d, k0); load_vec_nc(V + (int64_t)ta * p.d, v0); }
+    if (tb < end) { load_vec_nc(K + (int64_t)tb * p.d, k1); load_vec_nc(V + (int64_t)tb * p.d, v1); }
+  };
+  fetch(start, ka, kb, xa, xb);
+  for (int t0 = start; t0 < end; t0 += STEP) {
+    if (t0 + STEP < end) fetch(t0 + STEP, nka, nkb, nxa, nxb);
+    const bool va = t0 + grp < end, vb = t0 + KPI + grp < end;
     float sa = 0.0f, sb = 0.0f;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) { sa = fmaf(qv[e], ka[e], sa); sb = fmaf(qv[e], kb[e], sb); }
@@ -192,6 +203,8 @@ __global__ void attn_dec_kernel(AttnDecParams p) {
       for (int e = 0; e < VEC; ++e) o[e] = fmaf(pb, xb[e], fmaf(pa, xa[e], o[e] * alpha));
       m = m_new;
     }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { ka[e] = nka[e]; kb[e] = nkb[e]; xa[e] = nxa[e]; xb[e] = nxb[e]; }
   }
   // merge the key sub-groups of the warp
 #pragma unroll
@@ -217,7 +230,178 @@ __global__ void attn_dec_kernel(AttnDecParams p) {
   if (lane == 0) { p.part_ml[pi * 2] = m; p.part_ml[pi * 2 + 1] = l; }
 }
 
+// Streaming variant for long, fixed-length ranges (cross-attention): the K and
+// V rows of a CTA's key range are contiguous in the cache ([keys, d]), so a
+// producer warp moves them into a ring of shared-memory stages with bulk
+// asynchronous copies (cp.async.bulk + mbarrier transaction counts) and the H
+// head warps consume them from shared memory.  Bytes in flight per SM are set
+// by the ring (STAGES x 2 x SK x d elements), not by registers.
+// Block = (H + 1) warps; grid = (splits, rows).  Waits are bounded.
+constexpr int ATT_STAGES = 4;
+constexpr long long ATT_WAIT_CYCLES = 2000000000ll;
+
+__device__ __forceinline__ uint32_t att_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, DevStatus* status) {
+  const uint32_t a = att_smem_u32(bar);
+  const long long t0 = clock64();
+  for (int spin = 0;; ++spin) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((spin & 63) == 63) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > ATT_WAIT_CYCLES) {
+        *abort_flag = 1;
+        if (status) { atomicCAS(&status->code, 0, WDZ_ETIMEOUT); status->detail = 1000000 + (int)blockIdx.x; }
+        return false;
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p, DevStatus* status) {
+  constexpr int VEC = Vec<T>::N;
+  constexpr int LPK = HD / VEC;
+  constexpr int KPI = 32 / LPK;
+  constexpr int SK = 2 * KPI;      // keys per stage: one consumer iteration
+  extern __shared__ __align__(128) uint8_t att_smem[];
+  const int H = (blockDim.x >> 5) - 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t half_bytes = (size_t)SK * p.d * sizeof(T);          // K (or V) bytes of one stage
+  uint64_t* bars = reinterpret_cast<uint64_t*>(att_smem + ATT_STAGES * 2 * half_bytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + ATT_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * ATT_STAGES);
+
+  const int r = blockIdx.y, split = blockIdx.x;
+  const int slot = p.slots[r];
+  int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
+  len = len > p.S ? p.S : len;
+  const int start = split * p.chunk;
+  const bool active = slot >= 0 && slot < p.n_slots && start < len;   // uniform over the CTA
+  if (!active) return;
+  const int end = min(len, start + p.chunk);
+  const int n_iter = (end - start + SK - 1) / SK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ATT_STAGES; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(att_smem_u32(full + i)), "r"(1));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(att_smem_u32(empty + i)), "r"(H));
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int64_t row_base = (((int64_t)p.layer * p.n_slots + slot) * p.S) * p.d;
+  if (warp == H) {
+    if (lane == 0) {
+      const T* Kg = reinterpret_cast<const T*>(p.cache_k) + row_base;
+      const T* Vg = reinterpret_cast<const T*>(p.cache_v) + row_base;
+      for (int it = 0; it < n_iter; ++it) {
+        const int stage = it % ATT_STAGES;
+        const uint32_t phase = (it / ATT_STAGES) & 1;
+        if (!att_mbar_wait(empty + stage, phase ^ 1, abort_flag, status)) break;
+        const int t = start + it * SK;
+        const uint32_t bytes = (uint32_t)((size_t)min(SK, end - t) * p.d * sizeof(T));
+        uint8_t* dstk = att_smem + (size_t)stage * 2 * half_bytes;
+        const uint32_t bar = att_smem_u32(full + stage);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(att_smem_u32(dstk)), "l"(Kg + (int64_t)t * p.d), "r"(bytes), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(att_smem_u32(dstk + half_bytes)), "l"(Vg + (int64_t)t * p.d), "r"(bytes), "r"(bar) : "memory");
+      }
+    }
+    return;
+  }
+
+  const int h = warp;
+  const int piece = lane % LPK, grp = lane / LPK;
+  float qv[VEC];
+  {
+    const float* qp = p.q + (int64_t)r * p.ldq + h * HD + piece * VEC;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) qv[e] = qp[e] * QK_SCALE_LOG2E;
+  }
+  float m = -INFINITY, l = 0.0f, o[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) o[e] = 0.0f;
+  const int col = h * HD + piece * VEC;
+  bool ok = true;
+  for (int it = 0; it < n_iter; ++it) {
+    const int stage = it % ATT_STAGES;
+    const uint32_t phase = (it / ATT_STAGES) & 1;
+    ok = att_mbar_wait(full + stage, phase, abort_flag, status);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const T* Ks = reinterpret_cast<const T*>(att_smem + (size_t)stage * 2 * half_bytes);
+    const T* Vs = reinterpret_cast<const T*>(att_smem + (size_t)stage * 2 * half_bytes + half_bytes);
+    const int t0 = start + it * SK;
+    const bool va = t0 + grp < end, vb = t0 + KPI + grp < end;
+    float ka[VEC], kb[VEC], xa[VEC], xb[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ka[e] = kb[e] = xa[e] = xb[e] = 0.0f;
+    if (va) { load_vec(Ks + (size_t)grp * p.d + col, ka); load_vec(Vs + (size_t)grp * p.d + col, xa); }
+    if (vb) { load_vec(Ks + (size_t)(KPI + grp) * p.d + col, kb); load_vec(Vs + (size_t)(KPI + grp) * p.d + col, xb); }
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(att_smem_u32(empty + stage)) : "memory");
+    float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { sa = fmaf(qv[e], ka[e], sa); sb = fmaf(qv[e], kb[e], sb); }
+#pragma unroll
+    for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) {
+      sa += __shfl_xor_sync(0xffffffffu, sa, o2);
+      sb += __shfl_xor_sync(0xffffffffu, sb, o2);
+    }
+    if (!va) sa = -INFINITY;
+    if (!vb) sb = -INFINITY;
+    const float m_new = fmaxf(m, fmaxf(sa, sb));
+    if (m_new > -INFINITY) {
+      const float alpha = exp2f(m - m_new);
+      const float pa = exp2f(sa - m_new), pb = exp2f(sb - m_new);
+      l = l * alpha + pa + pb;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o[e] = fmaf(pb, xb[e], fmaf(pa, xa[e], o[e] * alpha));
+      m = m_new;
+    }
+  }
+  if (!ok) return;
+#pragma unroll
+  for (int o2 = LPK; o2 < 32; o2 <<= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o2);
+    const float l2 = __shfl_xor_sync(0xffffffffu, l, o2);
+    const float m_new = fmaxf(m, m2);
+    const float a1 = m_new > -INFINITY ? exp2f(m - m_new) : 0.0f;
+    const float a2 = m_new > -INFINITY ? exp2f(m2 - m_new) : 0.0f;
+    l = l * a1 + l2 * a2;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float o2v = __shfl_xor_sync(0xffffffffu, o[e], o2);
+      o[e] = o[e] * a1 + o2v * a2;
+    }
+    m = m_new;
+  }
+  const int64_t pi = ((int64_t)r * p.max_splits + split) * H + h;
+  if (grp == 0) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) p.part_o[pi * HD + piece * VEC + e] = o[e];
+  }
+  if (lane == 0) { p.part_ml[pi * 2] = m; p.part_ml[pi * 2 + 1] = l; }
+}
+
+template <typename T>
+inline size_t attn_dec_stream_smem(int d) {
+  return (size_t)ATT_STAGES * 2 * (2 * (32 / (HD / Vec<T>::N))) * d * sizeof(T) + 2 * ATT_STAGES * 8 + 16;
+}
+
 // Block = H warps; grid = rows.  Merges the splits that the row's length makes valid.
+template <typename TO>
 __global__ void attn_dec_combine_kernel(AttnDecParams p) {
   const int r = blockIdx.x;
   const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, H = blockDim.x >> 5;
@@ -238,9 +422,9 @@ __global__ void attn_dec_combine_kernel(AttnDecParams p) {
     o1 = fmaf(p.part_o[pi * HD + 32 + lane], w, o1);
   }
   const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-  float* dst = p.out + (int64_t)r * p.ldo + h * HD;
-  dst[lane] = o0 * inv;
-  dst[32 + lane] = o1 * inv;
+  TO* dst = reinterpret_cast<TO*>(p.out) + (int64_t)r * p.ldo + h * HD;
+  dst[lane] = from_f<TO>(o0 * inv);
+  dst[32 + lane] = from_f<TO>(o1 * inv);
 }
 
 }  // namespace wdz

@@ -18,6 +18,7 @@
 #include "common.cuh"
 #include "elementwise.cuh"
 #include "gemm_simt.cuh"
+#include "gemv_mma.cuh"
 #include "logmel.cuh"
 #include "rules.cuh"
 #ifdef WDZ_WITH_TC
@@ -79,6 +80,7 @@ struct wdz_engine {
   int max_emit = 0;
   int last_emit = 0;  // logit rows held from the last forward
   long long launches = 0;  // kernels enqueued since creation
+  bool stream_attn_ok = false;  // bulk-copy cross-attention kernel usable for this shape
 
   // optional per-kernel timing (wdz_profile): event pairs around selected launches
   struct Span { cudaEvent_t a, b; int kind; double work; };
@@ -123,7 +125,7 @@ namespace {
 size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
 
 int64_t part_entries_for(const wdz_config& c) {
-  int64_t a = 4ll * c.max_rows, b = (int64_t)c.max_rows + 512;
+  int64_t a = 8ll * c.max_rows, b = 2048;
   return a > b ? a : b;
 }
 
@@ -314,14 +316,25 @@ int cross_kv_impl(wdz_engine* e, const void* xa, const int* slot_ids, int B, cud
 template <typename T>
 int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool cross, cudaStream_t s) {
   const int H = e->cfg.n_text_head;
+  const bool stream = cross && e->stream_attn_ok;
   int splits;
-  if (cross) {
+  if (stream) {
+    // one CTA per SM at a time: pick the split count that fills whole waves best
+    int best = 1;
+    double best_util = 0.0;
+    for (int c = 1; c <= 24 && (int64_t)rows * c <= e->part_entries && max_len / c >= 32; ++c) {
+      const int ctas = rows * c, waves = (ctas + e->sm_count - 1) / e->sm_count;
+      const double util = (double)ctas / ((double)waves * e->sm_count);
+      if (util > best_util + 1e-9) { best_util = util; best = c; }
+    }
+    p.chunk = (max_len + best - 1) / best;
+  } else if (cross) {
     splits = (3 * e->sm_count + rows - 1) / rows;
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;
     p.chunk = ((max_len + splits - 1) / splits + 7) / 8 * 8;
   } else {
-    p.chunk = 128;
+    p.chunk = 64;
   }
   splits = (max_len + p.chunk - 1) / p.chunk;
   if ((int64_t)rows * splits > e->part_entries)
@@ -329,57 +342,109 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
   p.max_splits = splits;
   const int sp = e->span_begin(cross ? WDZ_PROF_CROSS_ATTN : WDZ_PROF_SELF_ATTN,
                                cross ? 2.0 * rows * max_len * p.d * sizeof(T) : 0.0, s);
-  attn_dec_kernel<T><<<dim3(splits, rows), H * 32, 0, s>>>(p);
+  if (stream) {
+    attn_dec_stream_kernel<T><<<dim3(splits, rows), (H + 1) * 32, attn_dec_stream_smem<T>(p.d), s>>>(p, e->status);
+  } else {
+    int hpc = 1;  // heads per CTA: the largest divisor of H up to 5, so that several CTAs share an SM
+    for (int c = 2; c <= 5; ++c) if (H % c == 0) hpc = c;
+    attn_dec_kernel<T><<<dim3(splits, rows, H / hpc), hpc * 32, 0, s>>>(p);
+  }
   e->span_end(sp, s);
-  attn_dec_combine_kernel<<<rows, H * 32, 0, s>>>(p);
+  attn_dec_combine_kernel<T><<<rows, H * 32, 0, s>>>(p);
   e->launches += 1;
   WDZ_LAUNCH_CHECK(e, "attn_dec");
   return WDZ_OK;
 }
 
+// bf16 decode product on the tensor cores (x bf16 [M, K], W bf16 [N, K]).
+template <int EPI, bool OUT_BF16>
+int launch_gemv_mma(wdz_engine* e, const GemvMmaParams& p, cudaStream_t s) {
+  const int sp = e->span_begin(p.W == e->tok_emb ? WDZ_PROF_LM_HEAD : WDZ_PROF_DEC_GEMM, 2.0 * p.N * p.K, s);
+  gemv_mma_kernel<EPI, OUT_BF16><<<(p.N + 15) / 16, 256, 0, s>>>(p);
+  e->span_end(sp, s);
+  WDZ_LAUNCH_CHECK(e, "gemv_mma");
+  return WDZ_OK;
+}
+
+GemvMmaParams mma_params(const void* x, int64_t ldx, const void* W, const void* bias, void* y, int64_t ldy, int M,
+                         int N, int K) {
+  GemvMmaParams p{};
+  p.x = (const bf16*)x; p.ldx = ldx; p.W = (const bf16*)W; p.bias = (const bf16*)bias; p.y = y; p.ldy = ldy;
+  p.M = M; p.N = N; p.K = K;
+  return p;
+}
+
 // tokens/slots/positions: device int32 [n].  Logits of the emit rows land in e->logits.
+// Activations between kernels (LayerNorm output, attention output, MLP hidden)
+// are stored in T; the residual stream, q/k/v of the new rows and the logits stay fp32.
 template <typename T>
 int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const int* positions, int n,
                       const int* emit_rows, int n_emit, cudaStream_t s) {
+  constexpr bool kBf16 = sizeof(T) == 2;
   const wdz_config& c = e->cfg;
   const int d = c.n_text_state;
   int rc;
+  T* xn = (T*)e->dxn;
+  T* ao = (T*)e->dao;
+  T* hid = (T*)e->dh;
   embed_kernel<T><<<n, 256, 0, s>>>(tokens, positions, (const T*)e->tok_emb, (const T*)e->dec_pos, e->dx, n, d,
                                      c.n_vocab, c.n_text_ctx);
   WDZ_LAUNCH_CHECK(e, "embed");
   AttnDecParams ap{};
   ap.n_slots = c.n_slots; ap.d = d; ap.slots = slots;
-  ap.part_o = e->part_o; ap.part_ml = e->part_ml; ap.out = e->dao; ap.ldo = d;
+  ap.part_o = e->part_o; ap.part_ml = e->part_ml; ap.out = ao; ap.ldo = d;
+  // y = epi(x W^T + b) with x in T; RESID accumulates into the fp32 residual stream
+  auto gemm = [&](int epi, const T* x, int64_t ldx, const void* W, const void* bias, void* y, int64_t ldy, int M,
+                  int N, int K) -> int {
+    if constexpr (kBf16) {
+      GemvMmaParams p = mma_params(x, ldx, W, bias, y, ldy, M, N, K);
+      switch (epi) {
+        case EPI_STORE: return launch_gemv_mma<EPI_STORE, false>(e, p, s);
+        case EPI_RESID: return launch_gemv_mma<EPI_RESID, false>(e, p, s);
+        case EPI_GELU: return launch_gemv_mma<EPI_GELU, true>(e, p, s);
+        default: return e->fail(WDZ_EINVAL, "bad decode epilogue %d", epi);
+      }
+    } else {
+      return dec_gemm<T>(e, epi, (const float*)x, ldx, W, bias, (float*)y, ldy, M, N, K, nullptr, s);
+    }
+  };
   for (int l = 0; l < c.n_text_layer; ++l) {
     const LayerW& w = e->dec[l];
-    if ((rc = launch_ln<T, float>(e, e->dx, d, nullptr, w.ln1_w, w.ln1_b, e->dxn, d, n, d, s))) return rc;
-    if ((rc = dec_gemm<T>(e, EPI_STORE, e->dxn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d, nullptr, s))) return rc;
-    kv_append_kernel<T><<<n, 256, 0, s>>>(e->dqkv, slots, positions, (T*)e->self_k, (T*)e->self_v, l, c.n_slots,
-                                           c.max_tokens, d, n);
-    WDZ_LAUNCH_CHECK(e, "kv_append");
+    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln1_w, w.ln1_b, xn, d, n, d, s))) return rc;
+    if constexpr (kBf16) {
+      // fused QKV projection whose epilogue appends K and V to the slot cache
+      GemvMmaParams p = mma_params(xn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d);
+      p.cache_k = (bf16*)e->self_k; p.cache_v = (bf16*)e->self_v; p.slots = slots; p.positions = positions;
+      p.layer = l; p.n_slots = c.n_slots; p.S = c.max_tokens; p.d = d;
+      if ((rc = launch_gemv_mma<EPI_QKV_CACHE, false>(e, p, s))) return rc;
+    } else {
+      if ((rc = gemm(EPI_STORE, xn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d))) return rc;
+      kv_append_kernel<T><<<n, 256, 0, s>>>(e->dqkv, slots, positions, (T*)e->self_k, (T*)e->self_v, l, c.n_slots,
+                                             c.max_tokens, d, n);
+      WDZ_LAUNCH_CHECK(e, "kv_append");
+    }
     ap.layer = l;
     ap.q = e->dqkv; ap.ldq = 3 * d; ap.cache_k = e->self_k; ap.cache_v = e->self_v; ap.S = c.max_tokens;
     ap.positions = positions; ap.fixed_len = 0;
     if ((rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
-    if ((rc = dec_gemm<T>(e, EPI_RESID, e->dao, d, w.out_w, w.out_b, e->dx, d, n, d, d, nullptr, s))) return rc;
+    if ((rc = gemm(EPI_RESID, ao, d, w.out_w, w.out_b, e->dx, d, n, d, d))) return rc;
 
-    if ((rc = launch_ln<T, float>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, e->dxn, d, n, d, s))) return rc;
-    if ((rc = dec_gemm<T>(e, EPI_STORE, e->dxn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, nullptr, s))) return rc;
+    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s))) return rc;
+    if ((rc = gemm(EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d))) return rc;
     ap.q = e->dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
     ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
     if ((rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
-    if ((rc = dec_gemm<T>(e, EPI_RESID, e->dao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d, nullptr, s))) return rc;
+    if ((rc = gemm(EPI_RESID, ao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d))) return rc;
 
-    if ((rc = launch_ln<T, float>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, e->dxn, d, n, d, s))) return rc;
-    if ((rc = dec_gemm<T>(e, EPI_GELU, e->dxn, d, w.fc1_w, w.fc1_b, e->dh, 4 * d, n, 4 * d, d, nullptr, s))) return rc;
-    if ((rc = dec_gemm<T>(e, EPI_RESID, e->dh, 4 * d, w.fc2_w, w.fc2_b, e->dx, d, n, d, 4 * d, nullptr, s))) return rc;
+    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, xn, d, n, d, s))) return rc;
+    if ((rc = gemm(EPI_GELU, xn, d, w.fc1_w, w.fc1_b, hid, 4 * d, n, 4 * d, d))) return rc;
+    if ((rc = gemm(EPI_RESID, hid, 4 * d, w.fc2_w, w.fc2_b, e->dx, d, n, d, 4 * d))) return rc;
   }
   bump_seqlens_kernel<<<(n + 255) / 256, 256, 0, s>>>(slots, positions, e->seq_lens, n, c.n_slots);
   WDZ_LAUNCH_CHECK(e, "bump_seqlens");
   // final LayerNorm on the emit rows only, then the tied LM head (model.py:609-613)
-  if ((rc = launch_ln<T, float>(e, e->dx, d, emit_rows, e->dec_ln_w, e->dec_ln_b, e->dxn, d, n_emit, d, s))) return rc;
-  if ((rc = dec_gemm<T>(e, EPI_STORE, e->dxn, d, e->tok_emb, nullptr, e->logits, c.n_vocab, n_emit, c.n_vocab, d,
-                        nullptr, s))) return rc;
+  if ((rc = launch_ln<T, T>(e, e->dx, d, emit_rows, e->dec_ln_w, e->dec_ln_b, xn, d, n_emit, d, s))) return rc;
+  if ((rc = gemm(EPI_STORE, xn, d, e->tok_emb, nullptr, e->logits, c.n_vocab, n_emit, c.n_vocab, d))) return rc;
   e->last_emit = n_emit;
   return WDZ_OK;
 }
@@ -605,6 +670,22 @@ int wdz_finalize(wdz_engine* e) {
 #ifdef WDZ_WITH_TC
   if ((rc = gemm_tc_init(e)) != WDZ_OK) return rc;
 #endif
+  {
+    const size_t need = c.dtype == WDZ_BF16 ? attn_dec_stream_smem<bf16>(c.n_text_state)
+                                            : attn_dec_stream_smem<float>(c.n_text_state);
+    e->stream_attn_ok = c.n_text_head <= 20 && need <= 227 * 1024 && !(c.flags & WDZ_FLAG_NO_BULK_COPY);
+    if (e->stream_attn_ok) {
+      cudaError_t ce2 = c.dtype == WDZ_BF16
+          ? cudaFuncSetAttribute(attn_dec_stream_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need)
+          : cudaFuncSetAttribute(attn_dec_stream_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+      if (ce2 != cudaSuccess) {
+        cudaGetLastError();
+        return e->fail(WDZ_ECUDA, "attn_dec_stream smem attribute: %s", cudaGetErrorString(ce2));
+      }
+    }
+  }
+  if (c.dtype == WDZ_BF16 && c.n_text_state % 256)
+    return e->fail(WDZ_EINVAL, "the bf16 decoder needs n_text_state to be a multiple of 256 (got %d)", c.n_text_state);
   e->finalized = true;
   return WDZ_OK;
 }
