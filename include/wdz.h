@@ -142,6 +142,13 @@ int wdz_encode(wdz_engine* e, const float* mel_dev, int B, void* xa_out_dev, wdz
 int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev, const void* bias_dev, int N,
                int gelu, void* y_dev, int cuda_cores_only, wdz_stream s);
 
+/* Encoder self-attention alone (MultiHeadAttention.qkv_attention, model.py:276-298):
+ * qkv_dev [B, n_audio_ctx, 3 * n_audio_state] (q | k | v per row, cfg.dtype) ->
+ * out_dev [B, n_audio_ctx, n_audio_state]; non-causal, scale 1/8.
+ * cuda_cores_only != 0 keeps a bf16 call off the tcgen05 kernel. */
+int wdz_encoder_attention(wdz_engine* e, const void* qkv_dev, int B, void* out_dev, int cuda_cores_only,
+                          wdz_stream s);
+
 /* ---- decoder ----------------------------------------------------------- */
 /* Cross K/V of all layers for B windows into their slots
  * (WhisperDRZ.prefill_flash, model.py:852-855). slot_ids_dev int32 [B]. */

@@ -263,3 +263,79 @@ def test_tensor_core_linear_matches_fp32_reference(small_bf16, M, N, K, gelu):
     assert err < 6e-3, err
     got_cc = e.linear(x, w, b, gelu=gelu, cuda_cores_only=True).float().cpu()
     assert (got - got_cc).abs().max() / ref.abs().max() < 6e-3
+
+
+def test_decoder_bf16_many_rows_tensor_core_path():
+    """More than 16 token rows per call take the operand-swapped tcgen05 product
+    (prefill of ~150 prompt rows, then decode steps over 20 slots at different
+    depths).  Two checks: (1) it agrees with the mma.sync path of the same
+    engine (same bf16 operands, fp32 accumulation; bf16 re-rounding of the
+    activations between layers amplifies order noise: within 2e-2 x logit RMS);
+    (2) both stay within 5e-2 x logit RMS of the fp32 oracle - the max is taken
+    over 20 rows x 51866 logits of a 2-layer random model fed random prompt
+    ids, where bf16 rounding of weights alone gives 3-4e-2 on either path."""
+    from whisperdrz_b200 import capi
+    e, dims, sd = _engine("test-small", torch.bfloat16, n_slots=24, max_clips=2, max_rows=256)
+    e2, _, _ = _engine("test-small", torch.bfloat16, n_slots=24, max_clips=2, max_rows=256,
+                       flags=capi.FLAG_NO_TENSOR_CORE)
+    rng = np.random.default_rng(11)
+    audio = synth.clips([31, 32])
+    mel = _oracle_mel(audio)
+    xa_ref = oracle.encoder(sd, mel, dims.n_audio_layer, dims.n_audio_head)
+    n = 20
+    slots = list(range(2, 2 + n))
+    xa_rows = xa_ref[[i % 2 for i in range(n)]]
+    prompts = [list(map(int, rng.integers(0, 50000, int(rng.integers(3, 13))))) for _ in range(n)]
+    dec = oracle.SlotDecoder(sd, dims.n_text_layer, dims.n_text_head, 24, dims.n_text_ctx)
+    dec.set_cross(xa_rows, slots)
+    dec.reset(slots)
+    ref = torch.stack([dec.forward(torch.tensor([p]), [s])[0, -1] for p, s in zip(prompts, slots)])
+    tok, sl, pos, emit = [], [], [], []
+    for p, s in zip(prompts, slots):
+        for j, t in enumerate(p):
+            tok.append(t); sl.append(s); pos.append(j)
+        emit.append(len(tok) - 1)
+    assert len(tok) > 100
+    rms = ref.pow(2).mean().sqrt()
+    got = []
+    for eng in (e, e2):
+        for i in range(0, n, 2):   # at most max_clips windows per cross-K/V call
+            eng.cross_kv(xa_rows[i: i + 2].cuda(), slots[i: i + 2])
+        eng.slot_reset(slots)
+        got.append(eng.forward_rows(tok, sl, pos, emit_rows=emit).cpu())
+    assert (got[0] - got[1]).abs().max() < 2e-2 * rms
+    assert (got[0] - ref).abs().max() < 5e-2 * rms
+    cur = ref.argmax(-1)
+    for _ in range(3):
+        ref = torch.stack([dec.forward(cur[i].view(1, 1), [s])[0, 0] for i, s in enumerate(slots)])
+        _, lg = e.decode_step(cur, slots, want_logits=True)
+        _, lg2 = e2.decode_step(cur, slots, want_logits=True)
+        assert (lg - lg2).abs().max().cpu() < 2e-2 * rms
+        assert (lg.cpu() - ref).abs().max() < 5e-2 * rms
+        cur = ref.argmax(-1)
+    e.device_status()
+    assert [e.seq_lens()[s] for s in slots] == [len(p) + 3 for p in prompts]
+    e.close()
+    e2.close()
+
+
+def test_tensor_core_encoder_attention_matches_fp32_reference(small_bf16):
+    """tcgen05 flash attention (S and PV on the tensor cores, P through TMEM)
+    against softmax(q k^T / 8) v in fp32 on the same bf16 inputs.  Tolerance:
+    bf16 rounding of P and of the output (2^-8 relative each)."""
+    e, dims, _ = small_bf16
+    g = torch.Generator().manual_seed(5)
+    B, T, d, H = 2, dims.n_audio_ctx, dims.n_audio_state, dims.n_audio_head
+    qkv = torch.randn(B, T, 3 * d, generator=g)
+    qkv[..., :d] *= 2.0          # sharper softmax than unit-variance scores
+    qkv = qkv.bfloat16()
+    q, k, v = (t.float().view(B, T, H, 64).permute(0, 2, 1, 3) for t in qkv.split(d, dim=-1))
+    ref = torch.softmax(q @ k.transpose(-1, -2) / 8.0, -1) @ v
+    ref = ref.permute(0, 2, 1, 3).reshape(B, T, d)
+    got = e.encoder_attention(qkv).float().cpu()
+    e.device_status()
+    err = (got - ref).abs().max() / ref.abs().max()
+    assert err < 1.5e-2, err
+    assert (got - ref).norm() / ref.norm() < 6e-3
+    got_cc = e.encoder_attention(qkv, cuda_cores_only=True).float().cpu()
+    assert (got_cc - ref).abs().max() / ref.abs().max() < 1.5e-2

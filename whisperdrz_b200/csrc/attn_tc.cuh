@@ -1,0 +1,230 @@
+// Encoder self-attention on tcgen05 (non-causal, head_dim 64, bf16 in, fp32
+// softmax): MultiHeadAttention.qkv_attention, src/whisperdrz/model.py:276-298.
+//
+// One CTA per (128-query tile, head, window); two CTAs share an SM so that one
+// CTA's softmax overlaps the other's MMAs.  Per 128-key tile:
+//   S  = Q K^T        tcgen05.mma, both operands from 128-byte-swizzled shared
+//                     memory (TMA), fp32 accumulator in TMEM columns [0,128)
+//   P  = exp2(S*c - m) four softmax warps, one query row per thread: two passes
+//                     of tcgen05.ld over S (row max, then exponentials), P
+//                     packed to bf16 and written back to TMEM columns [128,192)
+//                     with tcgen05.st
+//   PV = P V          tcgen05.mma with the A operand read from TMEM and V used
+//                     as an MN-major shared-memory operand (the [key][dim] tile
+//                     exactly as TMA delivers it), result in columns [192,256)
+// The running output stays in registers: O = (O + PV) * alpha, so no TMEM
+// read-modify-write is needed.  K/V tiles are double-buffered.  Every mbarrier
+// wait is bounded and reports WDZ_ETIMEOUT instead of hanging.
+#pragma once
+#include "attention.cuh"
+#include "gemm_tc.cuh"
+
+namespace wdz {
+namespace atc {
+
+using namespace tc;
+
+constexpr int QT = 128, KT = 128, KV_STAGES = 2;
+constexpr int TILE_BYTES = 128 * 128;           // 128 rows x 64 bf16
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 256 + 1024;
+constexpr int COL_S = 0, COL_P = 128, COL_O = 192, TMEM_COLS = 256;
+constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KT >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
+constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
+
+struct AttnTcParams {
+  bf16* out;            // [B * T, d]
+  int T, d, n_kv;       // n_kv = ceil(T / 128)
+  DevStatus* status;
+};
+
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+__global__ void __launch_bounds__(192, 2)
+attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = smem + TILE_BYTES;            // stage s: K at kv_s + s * 2 * TILE, V right after
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TILE_BYTES * (1 + 2 * KV_STAGES));
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                 // [2]
+  uint64_t* kv_empty = bars + 3;                // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* s_empty = bars + 6;
+  uint64_t* p_ready = bars + 7;
+  uint64_t* pv_full = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * QT, h = blockIdx.y, b = blockIdx.z;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < KV_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 128);
+    mbar_init(p_ready, 128);
+    mbar_init(pv_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmQKV) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_3d(q_s, &tmQKV, q_full, h * 64, q0, b);
+      for (int j = 0; j < p.n_kv; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t phase = (j / KV_STAGES) & 1;
+        if (!mbar_wait(kv_empty + st, phase ^ 1, abort_flag, p.status)) break;
+        uint8_t* k_dst = kv_s + st * 2 * TILE_BYTES;
+        mbar_expect_tx(kv_full + st, 2 * TILE_BYTES);
+        tma_load_3d(k_dst, &tmQKV, kv_full + st, p.d + h * 64, j * KT, b);
+        tma_load_3d(k_dst + TILE_BYTES, &tmQKV, kv_full + st, 2 * p.d + h * 64, j * KT, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
+      const uint32_t q_addr = smem_u32(q_s);
+      for (int j = 0; ok && j < p.n_kv; ++j) {
+        const int st = j % KV_STAGES;
+        if (!(ok = mbar_wait(kv_full + st, (j / KV_STAGES) & 1, abort_flag, p.status))) break;
+        if (!(ok = mbar_wait(s_empty, (j & 1) ^ 1, abort_flag, p.status))) break;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(kv_s + st * 2 * TILE_BYTES);
+        const uint32_t v_addr = k_addr + TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // contraction over the 64 head dims
+          umma_idesc(tmem_base + COL_S, umma_desc(q_addr + k * 32), umma_desc(k_addr + k * 32), IDESC_S, k != 0);
+        umma_commit(s_full);
+        if (!(ok = mbar_wait(p_ready, j & 1, abort_flag, p.status))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < KT / 16; ++k)  // contraction over the 128 keys; P holds two keys per TMEM column
+          umma_ts(tmem_base + COL_O, tmem_base + COL_P + k * 8, umma_desc(v_addr + k * 2048), IDESC_PV, k != 0);
+        umma_commit(pv_full);
+        umma_commit(kv_empty + st);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int q = q0 + row;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float m = -INFINITY, l = 0.0f, o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < p.n_kv; ++j) {
+      ok = mbar_wait(s_full, j & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int k0 = j * KT;
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + COL_S + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (k0 + c * 32 + i < p.T) mx = fmaxf(mx, v[i]);
+      }
+      const float m_new = fmaxf(m, mx * QK_SCALE_LOG2E);
+      const float alpha = exp2f(m - m_new);
+      if (j > 0) {
+        ok = mbar_wait(pv_full, (j - 1) & 1, abort_flag, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float v[32];
+          tmem_ld32(lane_addr + COL_O + c * 32, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + v[i]) * alpha;
+        }
+      }
+      float sum = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + COL_S + c * 32, v);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int kk = k0 + c * 32 + 2 * i;
+          const float p0 = kk < p.T ? exp2f(v[2 * i] * QK_SCALE_LOG2E - m_new) : 0.0f;
+          const float p1 = kk + 1 < p.T ? exp2f(v[2 * i + 1] * QK_SCALE_LOG2E - m_new) : 0.0f;
+          sum += p0 + p1;
+          pk[i] = pack_bf16(p0, p1);
+        }
+        tmem_st16(lane_addr + COL_P + c * 16, pk);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      l = l * alpha + sum;
+      m = m_new;
+      tc_fence_before();
+      mbar_arrive(s_empty);
+      mbar_arrive(p_ready);
+    }
+    if (ok) {
+      ok = mbar_wait(pv_full, (p.n_kv - 1) & 1, abort_flag, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      bf16* dst = p.out + ((int64_t)b * p.T + q) * p.d + h * 64;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + COL_O + c * 32, v);
+        if (q < p.T) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 t;
+            t.x = pack_bf16((o[c * 32 + 8 * g] + v[8 * g]) * inv, (o[c * 32 + 8 * g + 1] + v[8 * g + 1]) * inv);
+            t.y = pack_bf16((o[c * 32 + 8 * g + 2] + v[8 * g + 2]) * inv, (o[c * 32 + 8 * g + 3] + v[8 * g + 3]) * inv);
+            t.z = pack_bf16((o[c * 32 + 8 * g + 4] + v[8 * g + 4]) * inv, (o[c * 32 + 8 * g + 5] + v[8 * g + 5]) * inv);
+            t.w = pack_bf16((o[c * 32 + 8 * g + 6] + v[8 * g + 6]) * inv, (o[c * 32 + 8 * g + 7] + v[8 * g + 7]) * inv);
+            reinterpret_cast<uint4*>(dst + c * 32)[g] = t;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+}  // namespace atc
+}  // namespace wdz

@@ -23,6 +23,7 @@
 #include "rules.cuh"
 #ifdef WDZ_WITH_TC
 #include "gemm_tc.cuh"
+#include "attn_tc.cuh"
 #endif
 
 using namespace wdz;
@@ -31,6 +32,8 @@ using namespace wdz;
 struct wdz_engine;
 static int gemm_tc_init(wdz_engine* e);
 static int gemm_tc_launch(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s);
+static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& p, cudaStream_t s);
+static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int T, int d, int H, cudaStream_t s);
 #endif
 
 namespace {
@@ -254,6 +257,26 @@ int launch_ln(wdz_engine* e, const float* x, int64_t ldx, const int* row_idx, co
 }
 
 // ---- encoder ---------------------------------------------------------------
+// qkv T [B * Ta, 3d] -> out T [B * Ta, d]; tcgen05 kernel for bf16, CUDA cores otherwise.
+template <typename T>
+int enc_attention(wdz_engine* e, const void* qkv, void* out, int B, int Ta, int d, int H, cudaStream_t s) {
+  const int sp = e->span_begin(WDZ_PROF_ENC_ATTN, 4.0 * B * H * (double)Ta * Ta * HD, s);
+  int rc = 1;
+#ifdef WDZ_WITH_TC
+  if (sizeof(T) == 2 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) rc = attn_tc_launch(e, qkv, out, B, Ta, d, H, s);
+#endif
+  if (rc == 1) {
+    attn_enc_simt_kernel<T><<<dim3((Ta + 63) / 64, H, B), 256, attn_enc_simt_smem(), s>>>((const T*)qkv, (T*)out, Ta, d);
+    rc = WDZ_OK;
+    e->launches += 1;
+  }
+  e->span_end(sp, s);
+  if (rc != WDZ_OK) return rc;
+  cudaError_t ce = cudaGetLastError();
+  if (ce != cudaSuccess) return e->fail(WDZ_ECUDA, "attn_enc: %s", cudaGetErrorString(ce));
+  return WDZ_OK;
+}
+
 template <typename T>
 int encode_impl(wdz_engine* e, const float* mel, int B, void* xa_out, cudaStream_t s) {
   const wdz_config& c = e->cfg;
@@ -286,13 +309,7 @@ int encode_impl(wdz_engine* e, const float* mel, int B, void* xa_out, cudaStream
     const LayerW& w = e->enc[l];
     if ((rc = launch_ln<T, T>(e, e->x, d, nullptr, w.ln1_w, w.ln1_b, (T*)e->xn, d, M, d, s))) return rc;
     if ((rc = enc_gemm<T>(e, EPI_STORE, dense_params(e->xn, d, w.qkv_w, w.qkv_b, e->qkv, 3 * d, M, 3 * d, d), s))) return rc;
-    {
-      const int sp = e->span_begin(WDZ_PROF_ENC_ATTN, 4.0 * B * H * (double)Ta * Ta * HD, s);
-      attn_enc_simt_kernel<T><<<dim3((Ta + 63) / 64, H, B), 256, attn_enc_simt_smem(), s>>>(
-          (const T*)e->qkv, (T*)e->ao, Ta, d);
-      e->span_end(sp, s);
-    }
-    WDZ_LAUNCH_CHECK(e, "attn_enc");
+    if ((rc = enc_attention<T>(e, e->qkv, e->ao, B, Ta, d, H, s))) return rc;
     if ((rc = enc_gemm<T>(e, EPI_RESID, dense_params(e->ao, d, w.out_w, w.out_b, e->x, d, M, d, d), s))) return rc;
     if ((rc = launch_ln<T, T>(e, e->x, d, nullptr, w.ln2_w, w.ln2_b, (T*)e->xn, d, M, d, s))) return rc;
     if ((rc = enc_gemm<T>(e, EPI_GELU, dense_params(e->xn, d, w.fc1_w, w.fc1_b, e->hid, 4 * d, M, 4 * d, d), s))) return rc;
@@ -360,10 +377,18 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
 template <int EPI, bool OUT_BF16>
 int launch_gemv_mma(wdz_engine* e, const GemvMmaParams& p, cudaStream_t s) {
   const int sp = e->span_begin(p.W == e->tok_emb ? WDZ_PROF_LM_HEAD : WDZ_PROF_DEC_GEMM, 2.0 * p.N * p.K, s);
-  gemv_mma_kernel<EPI, OUT_BF16><<<(p.N + 15) / 16, 256, 0, s>>>(p);
+  int rc = 1;
+#ifdef WDZ_WITH_TC
+  if (p.M > 16 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) rc = gemm_tc_swap_launch(e, EPI, p, s);
+#endif
+  if (rc == 1) {
+    gemv_mma_kernel<EPI, OUT_BF16><<<(p.N + 15) / 16, 256, 0, s>>>(p);
+    e->span_end(sp, s);
+    WDZ_LAUNCH_CHECK(e, "gemv_mma");
+    return WDZ_OK;
+  }
   e->span_end(sp, s);
-  WDZ_LAUNCH_CHECK(e, "gemv_mma");
-  return WDZ_OK;
+  return rc;
 }
 
 GemvMmaParams mma_params(const void* x, int64_t ldx, const void* W, const void* bias, void* y, int64_t ldy, int M,
@@ -487,6 +512,65 @@ static int gemm_tc_init(wdz_engine* e) {
     cudaError_t ce = cudaGetLastError();
     return e->fail(WDZ_ECUDA, "gemm_tc smem attribute: %s", cudaGetErrorString(ce));
   }
+  if (cudaFuncSetAttribute(atc::attn_enc_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::SMEM_BYTES) !=
+      cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "attn_enc_tc smem attribute: %s", cudaGetErrorString(ce));
+  }
+  if (cudaFuncSetAttribute(tc::gemm_tc_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SW_SMEM_BYTES) !=
+      cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "gemm_tc_swap smem attribute: %s", cudaGetErrorString(ce));
+  }
+  return WDZ_OK;
+}
+
+static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int T, int d, int H, cudaStream_t s) {
+  if (((uintptr_t)qkv | (uintptr_t)out) & 15 || d % 8) return 1;
+  CUtensorMap mq;
+  if (!tc::make_map(&mq, qkv, (uint64_t)3 * d, (uint64_t)T, (uint64_t)B, (uint64_t)3 * d * 2, (uint64_t)T * 3 * d * 2,
+                    128, 3))
+    return 1;
+  atc::AttnTcParams p{};
+  p.out = (bf16*)out; p.T = T; p.d = d; p.n_kv = (T + atc::KT - 1) / atc::KT; p.status = e->status;
+  atc::attn_enc_tc_kernel<<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, p);
+  e->launches += 1;
+  return WDZ_OK;
+}
+
+// Decode-shaped product through the operand-swapped tcgen05 kernel.  Returns 1
+// when the shape is left to the mma.sync kernel.
+static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, cudaStream_t s) {
+  if (g.M < 1 || g.M > 256 || g.K % tc::BK) return 1;
+  if ((((uintptr_t)g.x | (uintptr_t)g.W) & 15) || (g.ldx * 2) % 16) return 1;
+  tc::TcSwapParams p{};
+  p.bias = g.bias; p.y = g.y; p.ldy = g.ldy; p.M = g.M; p.N = g.N; p.K = g.K;
+  p.mpad = (g.M + 31) / 32 * 32;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < p.mpad) p.tmem_cols <<= 1;
+  p.kblocks = g.K / tc::BK;
+  const int tiles = (g.N + tc::BM - 1) / tc::BM;
+  int ksplit = 1;
+  if (epi == EPI_RESID) {
+    ksplit = (e->sm_count + tiles - 1) / tiles;
+    if (ksplit > p.kblocks) ksplit = p.kblocks;
+    if (ksplit < 1) ksplit = 1;
+  }
+  p.kb_per_split = (p.kblocks + ksplit - 1) / ksplit;
+  ksplit = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
+  p.epi = epi == EPI_QKV_CACHE ? tc::EPI_SW_QKV_CACHE : epi;
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mpad >> 3) << 17) | ((uint32_t)(tc::BM >> 4) << 24);
+  p.cache_k = g.cache_k; p.cache_v = g.cache_v; p.slots = g.slots; p.positions = g.positions;
+  p.layer = g.layer; p.n_slots = g.n_slots; p.S = g.S; p.d = g.d;
+  p.status = e->status;
+  CUtensorMap mw, mx;
+  if (!tc::make_map(&mw, g.W, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * g.N, tc::BM, 2))
+    return 1;
+  if (!tc::make_map(&mx, g.x, (uint64_t)g.K, (uint64_t)g.M, 1, (uint64_t)g.ldx * 2, (uint64_t)g.ldx * 2 * g.M,
+                    (uint32_t)p.mpad, 2))
+    return 1;
+  tc::gemm_tc_swap_kernel<<<dim3(tiles, ksplit), tc::THREADS, tc::SW_SMEM_BYTES, s>>>(mw, mx, p);
+  WDZ_LAUNCH_CHECK(e, "gemm_tc_swap");
   return WDZ_OK;
 }
 
@@ -719,6 +803,20 @@ int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev
   const int saved = e->cfg.flags;
   if (cuda_cores_only) e->cfg.flags |= WDZ_FLAG_NO_TENSOR_CORE;
   rc = enc_gemm<bf16>(e, epi, p, st);
+  e->cfg.flags = saved;
+  return rc;
+}
+
+int wdz_encoder_attention(wdz_engine* e, const void* qkv_dev, int B, void* out_dev, int cuda_cores_only, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!qkv_dev || !out_dev || B < 1) return e->fail(WDZ_EINVAL, "wdz_encoder_attention: bad argument");
+  const wdz_config& c = e->cfg;
+  const int saved = e->cfg.flags;
+  if (cuda_cores_only) e->cfg.flags |= WDZ_FLAG_NO_TENSOR_CORE;
+  rc = c.dtype == WDZ_BF16
+           ? enc_attention<bf16>(e, qkv_dev, out_dev, B, c.n_audio_ctx, c.n_audio_state, c.n_audio_head, (cudaStream_t)s)
+           : enc_attention<float>(e, qkv_dev, out_dev, B, c.n_audio_ctx, c.n_audio_state, c.n_audio_head, (cudaStream_t)s);
   e->cfg.flags = saved;
   return rc;
 }

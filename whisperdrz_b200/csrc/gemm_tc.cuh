@@ -307,6 +307,154 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+// ---------------------------------------------------------------------------
+// Decode-shaped product on tcgen05 with the operands swapped:
+//   D[feature, row] = W[128-feature tile, K] . x[rows, K]^T
+// so that the 128-wide MMA M dimension is filled by output features and the
+// few dozen to 256 token rows form the MMA N dimension.  W is read from HBM
+// exactly once per call; the x tile (rows x 64 k, at most 32 KB) is re-staged
+// by TMA once per 128 features instead of once per 16.  grid = (feature
+// tiles, K splits); with more than one K split the partial sums are added to
+// the fp32 output with red.global.add (residual-stream epilogue only).
+// Epilogue thread = one feature (TMEM lane), columns = rows.
+// ---------------------------------------------------------------------------
+constexpr int SW_STAGES = 4;
+constexpr int SW_STAGE_BYTES = A_BYTES + 256 * BK * 2;   // W tile + up to 256 rows of x
+constexpr int SW_SMEM_BYTES = SW_STAGES * SW_STAGE_BYTES + 256 + 1024;
+constexpr int EPI_SW_QKV_CACHE = 16;
+
+struct TcSwapParams {
+  const bf16* bias; void* y; int64_t ldy;
+  int M, N, K;               // rows, features, contraction
+  int mpad;                  // rows padded to a multiple of 32 (MMA N)
+  int tmem_cols;             // power of two >= mpad, >= 32
+  int kb_per_split, kblocks;
+  int epi;                   // EPI_STORE (f32) | EPI_GELU (bf16 out) | EPI_RESID (f32 +=) | EPI_SW_QKV_CACHE
+  uint32_t idesc;
+  bf16* cache_k; bf16* cache_v; const int* slots; const int* positions;
+  int layer, n_slots, S, d;
+  DevStatus* status;
+};
+
+__device__ __forceinline__ void umma_idesc(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const TcSwapParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SW_STAGES * SW_STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + SW_STAGES;
+  uint64_t* acc_full = bars + 2 * SW_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SW_STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
+  const int kb0 = blockIdx.y * p.kb_per_split;
+  const int kb1 = min(p.kblocks, kb0 + p.kb_per_split);
+  const int nkb = kb1 - kb0;   // >= 1 by construction of the grid
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < SW_STAGES; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmW) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmX) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(p.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t stage_tx = A_BYTES + (uint32_t)p.mpad * BK * 2;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int stage = i % SW_STAGES;
+        const uint32_t phase = (i / SW_STAGES) & 1;
+        if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.status)) break;
+        uint8_t* w_dst = smem + stage * SW_STAGE_BYTES;
+        mbar_expect_tx(full + stage, stage_tx);
+        tma_load_2d(w_dst, &tmW, full + stage, (kb0 + i) * BK, tile * BM);
+        tma_load_2d(w_dst + A_BYTES, &tmX, full + stage, (kb0 + i) * BK, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        const int stage = i % SW_STAGES;
+        const uint32_t phase = (i / SW_STAGES) & 1;
+        if (!(ok = mbar_wait(full + stage, phase, abort_flag, p.status))) break;
+        tc_fence_after();
+        const uint32_t w_addr = smem_u32(smem + stage * SW_STAGE_BYTES);
+        const uint32_t x_addr = w_addr + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_idesc(tmem_base, umma_desc(w_addr + k * UMMA_K * 2), umma_desc(x_addr + k * UMMA_K * 2), p.idesc, (i | k) != 0);
+        umma_commit(empty + stage);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    const int quad = warp & 3;
+    bool ok = mbar_wait(acc_full, 0, abort_flag, p.status);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const int n = tile * BM + quad * 32 + lane;   // output feature of this thread
+      const bool n_ok = n < p.N;
+      float bias = 0.0f;
+      if (n_ok && p.bias && blockIdx.y == 0) bias = to_f(p.bias[n]);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < p.mpad; c += 32) {
+        float v[32];
+        tmem_ld32(taddr + c, v);
+        if (!n_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int m = c + j;
+          if (m >= p.M) break;
+          const float val = v[j] + bias;
+          if (p.epi == EPI_RESID) {
+            float* dst = reinterpret_cast<float*>(p.y) + (int64_t)m * p.ldy + n;
+            if (gridDim.y > 1) atomicAdd(dst, val); else *dst += val;
+          } else if (p.epi == EPI_GELU) {
+            reinterpret_cast<bf16*>(p.y)[(int64_t)m * p.ldy + n] = from_f<bf16>(gelu_erf(val));
+          } else if (p.epi == EPI_SW_QKV_CACHE && n >= p.d) {
+            const int s = p.slots[m], pos = p.positions[m];
+            if (s >= 0 && s < p.n_slots && pos >= 0 && pos < p.S) {
+              const bool is_v = n >= 2 * p.d;
+              bf16* dst = is_v ? p.cache_v : p.cache_k;
+              dst[(((int64_t)p.layer * p.n_slots + s) * p.S + pos) * p.d + (n - (is_v ? 2 : 1) * p.d)] = from_f<bf16>(val);
+            }
+          } else {
+            reinterpret_cast<float*>(p.y)[(int64_t)m * p.ldy + n] = val;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

@@ -250,6 +250,16 @@ class Engine:
                                         N, int(gelu), y.data_ptr(), int(cuda_cores_only), self._stream()))
         return y
 
+    def encoder_attention(self, qkv: torch.Tensor, cuda_cores_only: bool = False) -> torch.Tensor:
+        """qkv [B, n_audio_ctx, 3d] -> [B, n_audio_ctx, d] (non-causal, scale 1/8) in the engine dtype."""
+        qkv = qkv.to(device=self.device, dtype=self.dtype).contiguous()
+        B, T, d3 = qkv.shape
+        assert T == self.dims.n_audio_ctx and d3 == 3 * self.dims.n_audio_state and B <= self.max_clips
+        out = torch.empty(B, T, d3 // 3, dtype=self.dtype, device=self.device)
+        self._check(self.lib.wdz_encoder_attention(self.h, qkv.data_ptr(), B, out.data_ptr(), int(cuda_cores_only),
+                                                   self._stream()))
+        return out
+
     # --------------------------------------------------------------- decoder
     def cross_kv(self, xa: torch.Tensor, slots) -> None:
         xa = xa.to(self.dtype).contiguous()
