@@ -410,16 +410,30 @@ __global__ void attn_dec_combine_kernel(AttnDecParams p) {
   int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
   len = len > p.S ? p.S : len;
   const int nsplit = (len + p.chunk - 1) / p.chunk;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s)
-    M = fmaxf(M, p.part_ml[(((int64_t)r * p.max_splits + s) * H + h) * 2]);
-  float L = 0.0f, o0 = 0.0f, o1 = 0.0f;
-  for (int s = 0; s < nsplit; ++s) {
-    const int64_t pi = ((int64_t)r * p.max_splits + s) * H + h;
-    const float w = exp2f(p.part_ml[pi * 2] - M);
-    L = fmaf(p.part_ml[pi * 2 + 1], w, L);
-    o0 = fmaf(p.part_o[pi * HD + lane], w, o0);
-    o1 = fmaf(p.part_o[pi * HD + 32 + lane], w, o1);
+  const int64_t base = (int64_t)r * p.max_splits * H + h;   // entry of split s: base + s * H
+  float o0 = 0.0f, o1 = 0.0f, L = 0.0f, M = -INFINITY;
+  // splits in groups of 32: lanes fetch (m, l) of different splits in parallel
+  for (int s0 = 0; s0 < nsplit; s0 += 32) {
+    const int s = s0 + lane;
+    float ms = -INFINITY, ls = 0.0f;
+    if (s < nsplit) {
+      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + (base + (int64_t)s * H) * 2);
+      ms = ml.x; ls = ml.y;
+    }
+    const float M_new = fmaxf(M, warp_max(ms));
+    const float resc = exp2f(M - M_new);          // 0 on the first group
+    const float w = s < nsplit ? exp2f(ms - M_new) : 0.0f;
+    L = L * resc + warp_sum(ls * w);
+    o0 *= resc; o1 *= resc;
+    const int cnt = min(32, nsplit - s0);
+#pragma unroll 4
+    for (int i = 0; i < cnt; ++i) {
+      const float wi = __shfl_sync(0xffffffffu, w, i);
+      const float* po = p.part_o + (base + (int64_t)(s0 + i) * H) * HD;
+      o0 = fmaf(po[lane], wi, o0);
+      o1 = fmaf(po[32 + lane], wi, o1);
+    }
+    M = M_new;
   }
   const float inv = L > 0.0f ? 1.0f / L : 0.0f;
   TO* dst = reinterpret_cast<TO*>(p.out) + (int64_t)r * p.ldo + h * HD;

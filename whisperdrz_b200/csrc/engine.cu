@@ -84,6 +84,13 @@ struct wdz_engine {
   int last_emit = 0;  // logit rows held from the last forward
   long long launches = 0;  // kernels enqueued since creation
   bool stream_attn_ok = false;  // bulk-copy cross-attention kernel usable for this shape
+  // decode step as a CUDA graph, one per padded row count; inputs and outputs are staged
+  // through fixed workspace buffers so that a replay needs no re-capture
+  int *g_tokens = nullptr, *g_slots = nullptr, *g_next = nullptr;
+  wdz_rule_desc* g_rules = nullptr;
+  struct StepGraph { cudaGraphExec_t exec; long long launches; };
+  std::unordered_map<int, StepGraph> step_graphs;
+  cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
 
   // optional per-kernel timing (wdz_profile): event pairs around selected launches
   struct Span { cudaEvent_t a, b; int kind; double work; };
@@ -161,6 +168,10 @@ size_t carve(wdz_engine* e, char* base) {
   e->dq = (float*)take(sizeof(float) * R * dt);
   e->dh = (float*)take(sizeof(float) * R * 4 * dt);
   e->dpos = (int*)take(sizeof(int) * R);
+  e->g_tokens = (int*)take(sizeof(int) * (R + 8));
+  e->g_slots = (int*)take(sizeof(int) * (R + 8));
+  e->g_next = (int*)take(sizeof(int) * (R + 8));
+  e->g_rules = (wdz_rule_desc*)take(sizeof(wdz_rule_desc) * (R + 8));
   e->part_entries = part_entries_for(c);
   e->part_o = (float*)take(sizeof(float) * e->part_entries * H * HD);
   e->part_ml = (float*)take(sizeof(float) * e->part_entries * H * 2);
@@ -251,7 +262,7 @@ template <typename TP, typename TO>
 int launch_ln(wdz_engine* e, const float* x, int64_t ldx, const int* row_idx, const void* g, const void* b,
               TO* y, int64_t ldy, int rows, int d, cudaStream_t s) {
   if (rows <= 0) return WDZ_OK;
-  layernorm_kernel<TP, TO><<<(rows + 7) / 8, 256, 0, s>>>(x, ldx, row_idx, (const TP*)g, (const TP*)b, y, ldy, rows, d);
+  layernorm_kernel<TP, TO><<<(rows + 3) / 4, 128, 0, s>>>(x, ldx, row_idx, (const TP*)g, (const TP*)b, y, ldy, rows, d);
   WDZ_LAUNCH_CHECK(e, "layernorm");
   return WDZ_OK;
 }
@@ -333,16 +344,18 @@ int cross_kv_impl(wdz_engine* e, const void* xa, const int* slot_ids, int B, cud
 template <typename T>
 int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool cross, cudaStream_t s) {
   const int H = e->cfg.n_text_head;
-  const bool stream = cross && e->stream_attn_ok;
+  const bool stream = e->stream_attn_ok;
   int splits;
-  if (stream) {
+  if (stream && !cross) {
+    p.chunk = 128;   // lengths are only known on the device: fixed ranges, CTAs past a row's length exit at once
+  } else if (stream) {
     // one CTA per SM at a time: pick the split count that fills whole waves best
     int best = 1;
     double best_util = 0.0;
     for (int c = 1; c <= 24 && (int64_t)rows * c <= e->part_entries && max_len / c >= 32; ++c) {
       const int ctas = rows * c, waves = (ctas + e->sm_count - 1) / e->sm_count;
       const double util = (double)ctas / ((double)waves * e->sm_count);
-      if (util > best_util + 1e-9) { best_util = util; best = c; }
+      if (util > best_util + 0.03) { best_util = util; best = c; }
     }
     p.chunk = (max_len + best - 1) / best;
   } else if (cross) {
@@ -472,6 +485,26 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
   if ((rc = gemm(EPI_STORE, xn, d, e->tok_emb, nullptr, e->logits, c.n_vocab, n_emit, c.n_vocab, d))) return rc;
   e->last_emit = n_emit;
   return WDZ_OK;
+}
+
+// Copies the caller's step inputs into the fixed staging buffers and pads the
+// row count: padded rows carry slot -1 (every kernel skips them) and a forced
+// token so that the rule kernel never looks at their logits.
+__global__ void stage_step_kernel(const int* __restrict__ tokens, const int* __restrict__ slots,
+                                  const wdz_rule_desc* __restrict__ rules, int n, int npad,
+                                  int* __restrict__ g_tokens, int* __restrict__ g_slots,
+                                  wdz_rule_desc* __restrict__ g_rules) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;   // one thread per 32-bit word of a rule
+  const int r = i >> 5, w = i & 31;
+  if (r >= npad) return;
+  int* dst = reinterpret_cast<int*>(g_rules + r);
+  if (r < n) {
+    if (w == 0) { g_tokens[r] = tokens[r]; g_slots[r] = slots[r]; }
+    dst[w] = rules ? reinterpret_cast<const int*>(rules + r)[w] : (w == 0 ? -1 : 0);
+  } else {
+    if (w == 0) { g_tokens[r] = 0; g_slots[r] = -1; }
+    dst[w] = 0;   // forced_id = 0
+  }
 }
 
 int check_ready(wdz_engine* e) {
@@ -638,7 +671,11 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
 }
 
 int wdz_engine_destroy(wdz_engine* e) {
-  if (e) for (auto& sp : e->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
+  if (e) {
+    for (auto& sp : e->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
+    for (auto& g : e->step_graphs) cudaGraphExecDestroy(g.second.exec);
+    if (e->cap_stream) cudaStreamDestroy(e->cap_stream);
+  }
   delete e;
   return WDZ_OK;
 }
@@ -949,6 +986,17 @@ int wdz_prefill(wdz_engine* e, const void* xa_dev, const int32_t* window_slot_id
   return wdz_forward_rows(e, tokens_dev, slot_ids_dev, positions_dev, n, emit_rows_dev, n_emit, logits_out_dev, s);
 }
 
+// The work of one decode step on fixed buffers: positions from the slot
+// lengths, the forward over all rows, logit rules + argmax.
+static int decode_step_body(wdz_engine* e, const int* tokens, const int* slots, const wdz_rule_desc* rules, int n,
+                            int* next_out, cudaStream_t st) {
+  positions_from_seqlens_kernel<<<(n + 255) / 256, 256, 0, st>>>(slots, e->seq_lens, e->dpos, n, e->cfg.n_slots);
+  WDZ_LAUNCH_CHECK(e, "positions");
+  int rc = wdz_forward_rows(e, tokens, slots, e->dpos, n, nullptr, n, nullptr, (wdz_stream)st);
+  if (rc) return rc;
+  return rules_launch(e, e->logits, nullptr, rules, n, 1, next_out, st);
+}
+
 int wdz_decode_step(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slot_ids_dev, int n_active,
                     const wdz_rule_desc* rules_dev, int32_t* next_tokens_out_dev, float* logits_out_dev,
                     wdz_stream s) {
@@ -957,16 +1005,68 @@ int wdz_decode_step(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slo
   if (!tokens_dev || !slot_ids_dev || !next_tokens_out_dev || n_active < 0)
     return e->fail(WDZ_EINVAL, "wdz_decode_step: null argument");
   if (n_active == 0) return WDZ_OK;
-  if (n_active > e->cfg.max_rows || n_active > e->max_emit)
-    return e->fail(WDZ_ECAPACITY, "wdz_decode_step: %d rows > capacity %d", n_active,
-                   e->cfg.max_rows < e->max_emit ? e->cfg.max_rows : e->max_emit);
+  const int cap = e->cfg.max_rows < e->max_emit ? e->cfg.max_rows : e->max_emit;
+  if (n_active > cap) return e->fail(WDZ_ECAPACITY, "wdz_decode_step: %d rows > capacity %d", n_active, cap);
   cudaStream_t st = (cudaStream_t)s;
-  positions_from_seqlens_kernel<<<(n_active + 255) / 256, 256, 0, st>>>(slot_ids_dev, e->seq_lens, e->dpos, n_active,
-                                                                        e->cfg.n_slots);
-  WDZ_LAUNCH_CHECK(e, "positions");
-  if ((rc = wdz_forward_rows(e, tokens_dev, slot_ids_dev, e->dpos, n_active, nullptr, n_active, logits_out_dev, s)))
-    return rc;
-  return rules_launch(e, e->logits, nullptr, rules_dev, n_active, 1, next_tokens_out_dev, st);
+  const bool use_graph = !(e->cfg.flags & WDZ_FLAG_NO_GRAPH) && !e->profiling;
+  if (!use_graph) {
+    if ((rc = decode_step_body(e, tokens_dev, slot_ids_dev, rules_dev, n_active, next_tokens_out_dev, st))) return rc;
+  } else {
+    int npad = (n_active + 7) / 8 * 8;
+    if (npad > cap) npad = n_active;
+    stage_step_kernel<<<(npad * 32 + 255) / 256, 256, 0, st>>>(tokens_dev, slot_ids_dev, rules_dev, n_active, npad,
+                                                                 e->g_tokens, e->g_slots, e->g_rules);
+    WDZ_LAUNCH_CHECK(e, "stage_step");
+    auto it = e->step_graphs.find(npad);
+    if (it == e->step_graphs.end()) {
+      const long long before = e->launches;
+      cudaGraph_t graph = nullptr;
+      if (!e->cap_stream && cudaStreamCreateWithFlags(&e->cap_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaError_t ce0 = cudaGetLastError();
+        return e->fail(WDZ_ECUDA, "capture stream: %s", cudaGetErrorString(ce0));
+      }
+      if (cudaStreamBeginCapture(e->cap_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaError_t ce0 = cudaGetLastError();
+        return e->fail(WDZ_ECUDA, "graph capture begin: %s", cudaGetErrorString(ce0));
+      }
+      rc = decode_step_body(e, e->g_tokens, e->g_slots, e->g_rules, npad, e->g_next, e->cap_stream);
+      cudaError_t ce = cudaStreamEndCapture(e->cap_stream, &graph);
+      if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+      if (ce != cudaSuccess || !graph) {
+        cudaGetLastError();
+        return e->fail(WDZ_ECUDA, "graph capture end: %s", cudaGetErrorString(ce));
+      }
+      wdz_engine::StepGraph g{};
+      ce = cudaGraphInstantiate(&g.exec, graph, 0);
+      cudaGraphDestroy(graph);
+      if (ce != cudaSuccess) {
+        cudaGetLastError();
+        return e->fail(WDZ_ECUDA, "graph instantiate: %s", cudaGetErrorString(ce));
+      }
+      g.launches = e->launches - before;
+      e->launches = before;
+      it = e->step_graphs.emplace(npad, g).first;
+    }
+    if (cudaGraphLaunch(it->second.exec, st) != cudaSuccess) {
+      cudaError_t ce = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "graph launch: %s", cudaGetErrorString(ce));
+    }
+    e->launches += it->second.launches;
+    e->last_emit = npad;
+    if (cudaMemcpyAsync(next_tokens_out_dev, e->g_next, sizeof(int) * n_active, cudaMemcpyDeviceToDevice, st) !=
+        cudaSuccess) {
+      cudaError_t ce = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "token copy: %s", cudaGetErrorString(ce));
+    }
+  }
+  if (logits_out_dev) {
+    if (cudaMemcpyAsync(logits_out_dev, e->logits, sizeof(float) * (size_t)n_active * e->cfg.n_vocab,
+                        cudaMemcpyDeviceToDevice, st) != cudaSuccess) {
+      cudaError_t ce = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "logits copy: %s", cudaGetErrorString(ce));
+    }
+  }
+  return WDZ_OK;
 }
 
 int wdz_reargmax(wdz_engine* e, const int32_t* rows_dev, const wdz_rule_desc* rules_dev, int n, int32_t* out_dev,
