@@ -144,7 +144,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--model", default="large-v3")
-    ap.add_argument("--clips", type=int, default=32, help="30 s chunks per GPU per step")
+    ap.add_argument("--clips", type=int, default=256, help="30 s chunks per GPU per step")
     ap.add_argument("--new-tokens", type=int, default=224)
     ap.add_argument("--cpu-decode-steps", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -229,6 +229,9 @@ def main():
     eng.profile(False)
     peak, peak_kind = peaks()
     ca = prof["cross_attn"]
+    # dram read+write per row per launch of this kernel from the ncu capture summarised in
+    # profiles/attn_dec_stream_kernel_decode_32rows.md (32 rows: 245.944 MB + 4.606 MB); grows linearly with rows
+    traffic_per_row = (245.944064e6 + 4.605952e6) / 32
     per_launch_ms = ca["ms"] / max(ca["launches"], 1)
     per_launch_bytes = ca["work"] / max(ca["launches"], 1)
     achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms > 0 else 0.0
@@ -242,9 +245,10 @@ def main():
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
                 "gpu_launches": int(launches),
                 "decode_tokens_per_s": n_tok * world / (ms / 1e3),
-                "roofline": {"kernel": "attn_dec_kernel (decode cross-attention)", "bound": "hbm",
+                "roofline": {"kernel": "attn_dec_stream_kernel (decode cross-attention)", "bound": "hbm",
                              "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-                             "frac": achieved / peak, "traffic": None,
+                             "frac": achieved / peak,
+                             "traffic": traffic_per_row * per_launch_bytes / (2.0 * 1500 * 1280 * 2),
                              "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms},
                 "kernel_ms_one_step": shares}
         if world == 1 and not args.no_cpu_baseline:

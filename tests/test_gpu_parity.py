@@ -339,3 +339,34 @@ def test_tensor_core_encoder_attention_matches_fp32_reference(small_bf16):
     assert (got - ref).norm() / ref.norm() < 6e-3
     got_cc = e.encoder_attention(qkv, cuda_cores_only=True).float().cpu()
     assert (got_cc - ref).abs().max() / ref.abs().max() < 1.5e-2
+
+
+def test_drop_in_model_follows_the_reference_call_sequence(golden_dir):
+    """B200Model driven exactly as the reference Transcriber drives its model
+    (create_flash_kv, reset_flash_kv, encoder, prefill_flash, forward_flash with
+    positions read from self_kv[0].seq_lens) reproduces the reference recording."""
+    from whisperdrz_b200.model import B200Model
+    g = np.load(os.path.join(golden_dir, "model_test_small.npz"))
+    dims = ModelDimensions.from_name("test-small")
+    m = B200Model(dims, init_state_dict(dims, int(g["seed"])), dtype=torch.float32).cuda().eval()
+    B, n_steps = g["tokens"].shape
+    self_kv, cross_kv = m.create_flash_kv(B + 2, max_tokens=dims.n_text_ctx)
+    slots = torch.arange(1, B + 1, device="cuda")
+    m.reset_flash_kv(self_kv, cross_kv, slots)
+    m.decoder.cache_embedding_weight(torch.float32)
+    audio = synth.clips([int(s) for s in g["clip_seeds"]])
+    mel = m.engine.logmel(torch.from_numpy(audio).cuda())
+    xa = m.encoder(mel)
+    logits = m.prefill_flash(torch.from_numpy(g["prompt"]).cuda(), xa, self_kv, cross_kv, slots)[:, -1]
+    eot = TOK_EOT
+    toks = []
+    for _ in range(n_steps):
+        lg = logits.clone()
+        lg[:, eot] = float("-inf")
+        nxt = lg.argmax(-1)
+        toks.append(nxt.cpu())
+        pos = self_kv[0].seq_lens[slots]
+        logits = m.decoder.forward_flash(nxt[:, None], self_kv, cross_kv, pos, slot_indices=slots)[:, 0]
+    assert np.array_equal(torch.stack(toks, 1).numpy(), g["tokens"])
+    assert np.array_equal(self_kv[0].seq_lens.cpu().numpy()[1: B + 1], g["final_seq_lens"][1: B + 1])
+    m.engine.close()

@@ -1,0 +1,176 @@
+"""Host-only tests of the scheduler, the token-level rules and the multi-rank
+sharding, with a stub engine in place of the CUDA library (no GPU)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from whisperdrz_b200 import capi, rules
+from whisperdrz_b200.dims import TOK_EOT, TOK_TS_BEGIN
+from whisperdrz_b200.sharding import gather_results, shard, split_chunks
+from whisperdrz_b200.transcriber import Transcriber, rules_to_array
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class StubEngine:
+    """Deterministic stand-in with the Engine methods the scheduler calls.  Its
+    "model" proposes tokens from a per-slot counter and obeys the rule
+    descriptors the way the device kernel does (forced id, allowed range)."""
+    n_slots, max_tokens, max_clips = 4, 448, 2
+    device = torch.device("cpu")
+
+    def __init__(self):
+        self.calls = {"logmel": 0, "encode": 0, "prefill": 0, "decode": 0}
+        self.rows_per_step = []
+        self.count = {}
+
+    def logmel(self, buf, n_samples=None):
+        self.calls["logmel"] += 1
+        assert buf.shape[0] <= self.max_clips and buf.shape[1] == 480000
+        return torch.zeros(buf.shape[0], 128, 3000)
+
+    def encode(self, mel):
+        self.calls["encode"] += 1
+        return torch.zeros(mel.shape[0], 1500, 8)
+
+    def prefill(self, xa, slots, prompts):
+        self.calls["prefill"] += 1
+        for s in slots:
+            self.count[int(s)] = 0
+        return torch.zeros(len(slots), 16)
+
+    def _pick(self, slot, r):
+        r = [int(v) for v in r]
+        if r[0] >= 0:
+            return r[0]
+        self.count[slot] += 1
+        if r[1] == capi.MODE_ALL_EXCEPT_RANGE:
+            if r[16] and self.count[slot] % 7 == 0:
+                return TOK_EOT                       # cleared id: EOT allowed between pairs
+            return min(r[2] + 3, r[3] - 1)
+        if r[6] > r[5] and self.count[slot] % 3 == 0:
+            return r[6]                              # first allowed closing timestamp
+        return 1000 + self.count[slot]               # a text token
+
+    def rules_argmax(self, logits, rules):
+        arr = rules.numpy()
+        return torch.tensor([self._pick(i, arr[i]) for i in range(len(arr))], dtype=torch.int32)
+
+    def decode_step(self, tokens, slots, rules=None):
+        self.calls["decode"] += 1
+        self.rows_per_step.append(len(slots))
+        arr = rules.numpy()
+        return torch.tensor([self._pick(int(s), arr[i]) for i, s in enumerate(slots)], dtype=torch.int32)
+
+
+def _patch_rules_dev(tr):
+    tr._rules_dev = lambda rl: torch.from_numpy(rules_to_array(rl))
+
+
+def test_rule_state_machine_pairs_and_budget():
+    st = rules.RowState(max_new=5)
+    r = st.rule()
+    assert r["mode"] == capi.MODE_ALL_EXCEPT_RANGE and r["arg0"] == TOK_TS_BEGIN and r["arg1"] == TOK_TS_BEGIN + 51
+    st.update(TOK_TS_BEGIN + 10)                     # opening timestamp
+    r = st.rule()
+    assert r["table_bits"] == rules.BIT_SPECIAL | rules.BIT_TIMINGS      # a word must follow
+    st.update(500)
+    r = st.rule()
+    assert r["table_bits"] == rules.BIT_SPECIAL and r["prefix_end"] == TOK_TS_BEGIN + 11 and r["pen_ids"] == [500]
+    st.update(TOK_TS_BEGIN + 30)                     # closing timestamp
+    r = st.rule()
+    assert r["mode"] == capi.MODE_ALL_EXCEPT_RANGE and r["arg0"] == TOK_TS_BEGIN + 30 and r["clear_ids"] == [TOK_EOT]
+    st.update(TOK_TS_BEGIN + 31)
+    st.update(501)
+    assert st.rule() == {"forced_id": TOK_EOT}       # budget of 5 reached
+    st.update(TOK_EOT)
+    assert st.done
+    segs = rules.segments(st.tokens, offset=30.0)
+    assert segs == [{"start": 30.2, "end": 30.6, "tokens": [500]}]
+
+
+def test_rules_to_array_layout():
+    a = rules_to_array([{"forced_id": 9}, {"mode": 2, "arg0": 5, "arg1": 8, "table_bits": 3, "prefix_begin": 1,
+                                         "prefix_end": 4, "set_ids": [7], "clear_ids": [1, 2], "pen_ids": [3, 3, 4]}])
+    assert a.shape == (2, 32) and a[0, 0] == 9 and a[1, 0] == -1
+    assert list(a[1, 1:7]) == [2, 5, 8, 3, 1, 4]
+    assert a[1, 7] == 1 and a[1, 8] == 7 and a[1, 16] == 2 and list(a[1, 17:19]) == [1, 2]
+    assert a[1, 21] == 2 and list(a[1, 22:24]) == [3, 4]
+
+
+def test_scheduler_continuous_batching_with_stub_engine():
+    eng = StubEngine()
+    tr = Transcriber(eng, max_new_tokens=40)
+    _patch_rules_dev(tr)
+    audio = torch.randn(int(16000 * 30 * 9.5))       # 10 chunks for 4 slots
+    res = tr.transcribe(audio)
+    assert [r["id"] for r in res.raw_chunks] == [f"chunk_{i}" for i in range(10)]
+    assert res.raw_chunks[-1]["duration"] == pytest.approx(15.0)
+    assert all(r["stop_reason"] in ("eot", "max_tokens") for r in res.raw_chunks)
+    assert all(s.status == "ready" for s in tr.states) and not tr.pending_chunks
+    # slots are refilled as they finish: some steps run with fewer than 4 rows only at the tail
+    assert max(eng.rows_per_step) == 4 and eng.calls["prefill"] >= 3
+    # offsets are applied to the segments of later chunks
+    assert res.raw_chunks[3]["segments"][0]["start"] >= 90.0
+    assert abs(tr.seconds_processed - 285.0) < 1e-6
+    # timestamps inside a chunk never go backwards
+    for r in res.raw_chunks:
+        ts = [t for t in r["tokens"] if t >= TOK_TS_BEGIN]
+        assert ts == sorted(ts)
+
+
+def test_pipeline_call_and_flush():
+    eng = StubEngine()
+    tr = Transcriber(eng, max_new_tokens=12)
+    _patch_rules_dev(tr)
+    chunks = split_chunks(torch.randn(16000 * 70))
+    assert [c["duration"] for c in chunks] == [30.0, 30.0, 10.0]
+    assert tr(chunks[0]) is None                     # buffering: fewer chunks than free slots
+    out = list(tr.flush())
+    assert len(out) == 1 and out[0]["id"] == "chunk_0"
+    tr(chunks[1:])
+    assert {r["id"] for r in tr.flush()} == {"chunk_1", "chunk_2"}
+
+
+def test_sharding_is_a_partition():
+    chunks = [{"id": f"chunk_{i}"} for i in range(11)]
+    parts = [shard(chunks, r, 4) for r in range(4)]
+    assert sorted(c["id"] for p in parts for c in p) == sorted(c["id"] for c in chunks)
+    assert [len(p) for p in parts] == [3, 3, 3, 2]
+    assert gather_results(list(reversed(chunks)), 0, 1) == chunks
+
+
+WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+from test_scheduler_cpu import StubEngine, _patch_rules_dev
+from whisperdrz_b200.transcriber import Transcriber
+from whisperdrz_b200.sharding import transcribe_sharded
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+tr = Transcriber(StubEngine(), max_new_tokens=20); _patch_rules_dev(tr)
+torch.manual_seed(0)
+audio = torch.randn(16000 * 30 * 7)
+res = transcribe_sharded(tr, audio, rank, world)
+if rank == 0:
+    assert [r["id"] for r in res.raw_chunks] == [f"chunk_{i}" for i in range(7)], res.raw_chunks
+    print("GATHERED", len(res.raw_chunks), len(res.segments))
+else:
+    assert res is None
+dist.destroy_process_group()
+"""
+
+
+def test_two_rank_sharding_over_gloo(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29731")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29731", str(script), ROOT]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=240)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "GATHERED 7" in out.stdout

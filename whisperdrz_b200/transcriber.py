@@ -90,8 +90,7 @@ class Transcriber:
         self.seconds_processed = 0.0
         self.steps = 0
         self.launch_rows = 0
-        self._pin_rules = None
-        self._pin_tok = None
+        self._pin_audio = None
 
     # ------------------------------------------------------------------ public
     def transcribe(self, audio) -> TranscribeResults:
@@ -153,9 +152,21 @@ class Transcriber:
                 for i, s in enumerate(grp):
                     buf[i, : n[i]] = s.chunk["audio"][: n[i]]
             else:
-                host = torch.zeros(len(grp), 480000, dtype=torch.float32).pin_memory()
+                self._pin_audio = getattr(eng, "_pin_audio", None)
+                if self._pin_audio is None:      # one pinned staging buffer per engine, reused for every group
+                    self._pin_audio = torch.zeros(eng.max_clips, 480000, dtype=torch.float32)
+                    if dev.type == "cuda":
+                        self._pin_audio = self._pin_audio.pin_memory()
+                    try:
+                        eng._pin_audio = self._pin_audio
+                    except AttributeError:
+                        pass
+                elif dev.type == "cuda":
+                    torch.cuda.current_stream(dev).synchronize()   # the previous upload has left the buffer
+                host = self._pin_audio[: len(grp)]
                 for i, s in enumerate(grp):
                     host[i, : n[i]] = torch.as_tensor(s.chunk["audio"][: n[i]], dtype=torch.float32)
+                    host[i, n[i]:] = 0.0
                 buf = host.to(dev, non_blocking=True)
             mel = eng.logmel(buf, n_samples=n)
             xa = eng.encode(mel)
