@@ -132,6 +132,31 @@ int wdz_logmel(wdz_engine* e, const float* audio_dev, int64_t audio_stride,
                const int32_t* n_samples_dev, const int32_t* frame_offset_dev, int B,
                float* mel_out_dev, wdz_stream s);
 
+/* wdz_logmel for hosts that cannot hand the engine a workspace.  No counterpart
+ * in the reference (its front end runs in torch on the CPU and allocates
+ * freely).  Some embedders of this library run inside a process whose GPU
+ * memory is handed out in full to another pool at start-up (a serving process
+ * that gives everything to its KV-cache manager), or inside a loop where the
+ * device-wide stall of cudaMalloc / cudaFree is not acceptable; they can bind
+ * the weights and tables they already hold but have nothing left to lend as
+ * scratch.  This entry point therefore takes no workspace: the un-normalised
+ * log-mel and the per-clip maxima go into an array compiled into the library
+ * (WDZ_STATIC_MAX_CLIPS x WDZ_STATIC_MAX_MELS x 3000 floats, about 6.1 MB,
+ * resident on every GPU that loads the library until the process exits).  It
+ * calls no cudaMalloc, cudaFree or allocating library routine; wdz_set_workspace
+ * need not have been called.  Same arguments and results as wdz_logmel, with
+ * B <= WDZ_STATIC_MAX_CLIPS and cfg.n_mels <= WDZ_STATIC_MAX_MELS, otherwise
+ * WDZ_ECAPACITY.  The first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress); make that first call before any stream
+ * capture begins.  All calls share the one array: it keeps the previous
+ * call's contents (the maxima are re-initialised inside every call), and two
+ * calls that overlap on the GPU - different streams or engines - race on it. */
+#define WDZ_STATIC_MAX_CLIPS 4
+#define WDZ_STATIC_MAX_MELS 128
+int wdz_logmel_static(wdz_engine* e, const float* audio_dev, int64_t audio_stride,
+                      const int32_t* n_samples_dev, const int32_t* frame_offset_dev, int B,
+                      float* mel_out_dev, wdz_stream s);
+
 /* ---- encoder: AudioEncoder.forward (model.py:462-475) ------------------ */
 /* mel_dev f32 [B, n_mels, 3000] -> xa_out_dev [B, n_audio_ctx, n_audio_state] in cfg.dtype */
 int wdz_encode(wdz_engine* e, const float* mel_dev, int B, void* xa_out_dev, wdz_stream s);

@@ -60,6 +60,7 @@ SYMBOLS = {
     "wdz_profile": (I, [P, I]),
     "wdz_profile_read": (I, [P, I, C.POINTER(C.c_double), C.POINTER(I64), C.POINTER(C.c_double)]),
     "wdz_logmel": (I, [P, P, I64, P, P, I, P, P]),
+    "wdz_logmel_static": (I, [P, P, I64, P, P, I, P, P]),
     "wdz_encode": (I, [P, P, I, P, P]),
     "wdz_linear": (I, [P, P, I, I, P, P, I, I, P, I, P]),
     "wdz_encoder_attention": (I, [P, P, I, P, I, P]),

@@ -9,6 +9,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -905,6 +906,67 @@ int wdz_logmel(wdz_engine* e, const float* audio_dev, int64_t audio_stride, cons
   e->span_end(sp, st);
   e->launches += 2;
   WDZ_LAUNCH_CHECK(e, "logmel");
+  return WDZ_OK;
+}
+
+// ---- log-mel with built-in scratch -----------------------------------------
+// The two intermediates of the front end (un-normalised log-mel of every frame
+// and the per-clip maximum) normally live in the caller-provided workspace.
+// This variant keeps them in a fixed array that is part of the library image,
+// so it can serve hosts that have no workspace to give.  Every GPU that loads
+// the library carries the array (about 6.1 MB) until the process exits.
+#define WDZ_STATIC_MEL_FLOATS (WDZ_STATIC_MAX_CLIPS * WDZ_STATIC_MAX_MELS * MEL_MAX_FRAMES)
+static __device__ __align__(256) float g_static_mel_scratch[WDZ_STATIC_MEL_FLOATS + 64];
+static std::mutex g_static_mu;
+static float* g_static_mel_ptr[64] = {};   // device address of the array, per device ordinal
+
+int wdz_logmel_static(wdz_engine* e, const float* audio_dev, int64_t audio_stride, const int32_t* n_samples_dev,
+                      const int32_t* frame_offset_dev, int B, float* mel_out_dev, wdz_stream s) {
+  if (!e) return WDZ_EINVAL;
+  if (!e->finalized) return e->fail(WDZ_ESTATE, "engine not finalized");
+  if (!audio_dev || !n_samples_dev || !mel_out_dev || B < 0)
+    return e->fail(WDZ_EINVAL, "wdz_logmel_static: null argument");
+  if (B == 0) return WDZ_OK;
+  if (B > WDZ_STATIC_MAX_CLIPS)
+    return e->fail(WDZ_ECAPACITY, "wdz_logmel_static: %d clips, the built-in scratch holds at most %d", B,
+                   WDZ_STATIC_MAX_CLIPS);
+  if (e->cfg.n_mels > WDZ_STATIC_MAX_MELS)
+    return e->fail(WDZ_ECAPACITY, "wdz_logmel_static: %d mel bins, the built-in scratch holds at most %d",
+                   e->cfg.n_mels, WDZ_STATIC_MAX_MELS);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "wdz_logmel_static: cannot tell the current device");
+  }
+  if (dev != e->device)
+    return e->fail(WDZ_EINVAL, "wdz_logmel_static: device %d is current but the engine lives on %d", dev, e->device);
+  float* scratch = nullptr;
+  {
+    // set-up, once per device: the array's name is only a handle on the host,
+    // the kernels need its address in that device's memory
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_mel_ptr[dev]) {
+      void* p = nullptr;
+      cudaError_t ce = cudaGetSymbolAddress(&p, g_static_mel_scratch);
+      if (ce != cudaSuccess || !p) {
+        cudaGetLastError();
+        return e->fail(WDZ_ECUDA, "wdz_logmel_static: cudaGetSymbolAddress: %s", cudaGetErrorString(ce));
+      }
+      g_static_mel_ptr[dev] = (float*)p;
+    }
+    scratch = g_static_mel_ptr[dev];
+  }
+  float* raw = scratch;
+  int* clipmax = reinterpret_cast<int*>(scratch + WDZ_STATIC_MEL_FLOATS);
+  cudaStream_t st = (cudaStream_t)s;
+  // the per-clip maxima are the only state that must not survive from the previous call
+  logmel_init_max_kernel<<<1, 64, 0, st>>>(clipmax, B);
+  logmel_raw_kernel<<<dim3((MEL_MAX_FRAMES + MEL_FT - 1) / MEL_FT, B), 256, logmel_smem_bytes(), st>>>(
+      audio_dev, audio_stride, n_samples_dev, e->mel, e->cfg.n_mels, raw, clipmax);
+  logmel_finalize_kernel<<<dim3((MEL_MAX_FRAMES + 255) / 256, e->cfg.n_mels, B), 256, 0, st>>>(
+      raw, clipmax, n_samples_dev, frame_offset_dev, e->cfg.n_mels, mel_out_dev);
+  e->launches += 2;
+  WDZ_LAUNCH_CHECK(e, "logmel_static");
   return WDZ_OK;
 }
 

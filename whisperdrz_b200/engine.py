@@ -228,6 +228,30 @@ class Engine:
                                         None if fo is None else fo.data_ptr(), B, mel.data_ptr(), self._stream()))
         return mel
 
+    def logmel_static(self, audio: torch.Tensor, n_samples=None, frame_offset=None) -> torch.Tensor:
+        """``logmel`` through the entry point that brings its own scratch: for
+        embedders that cannot lend the engine a workspace (all GPU memory
+        already handed to another pool, or no tolerance for the stall of a
+        device allocation).  At most 4 clips per call; calls share one built-in
+        array, so do not overlap them on the GPU; make the first call on a
+        device before any stream capture."""
+        audio = audio.to(device=self.device, dtype=torch.float32)
+        if audio.dim() == 1:
+            audio = audio[None]
+        audio = audio.contiguous()
+        B, N = audio.shape
+        if N > 480000:
+            raise ValueError("a window holds at most 30 s (480000 samples)")
+        ns = self._i32([N] * B if n_samples is None else n_samples)
+        if int(ns.min()) < 400:
+            raise ValueError("clips shorter than 400 samples cannot be reflect-padded")
+        fo = None if frame_offset is None else self._i32(frame_offset)
+        mel = torch.empty(B, self.dims.n_mels, 3000, dtype=torch.float32, device=self.device)
+        self._check(self.lib.wdz_logmel_static(self.h, audio.data_ptr(), N, ns.data_ptr(),
+                                               None if fo is None else fo.data_ptr(), B, mel.data_ptr(),
+                                               self._stream()))
+        return mel
+
     # --------------------------------------------------------------- encoder
     def encode(self, mel: torch.Tensor) -> torch.Tensor:
         mel = mel.to(device=self.device, dtype=torch.float32).contiguous()
