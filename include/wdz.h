@@ -168,6 +168,13 @@ int wdz_encode(wdz_engine* e, const float* mel_dev, int B, void* xa_out_dev, wdz
 int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev, const void* bias_dev, int N,
                int gelu, void* y_dev, int cuda_cores_only, wdz_stream s);
 
+/* One nn.Linear as the decoder runs it for a handful of token rows
+ * (model.py:258-261 called from forward_flash): x_dev [M, K] in cfg.dtype,
+ * w_dev [N, K], optional bias -> y_dev f32 [M, N]; accumulate != 0 adds into
+ * y_dev (the residual-stream update of model.py:421-434) instead of storing. */
+int wdz_linear_rows(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev, const void* bias_dev, int N,
+                    int accumulate, float* y_dev, wdz_stream s);
+
 /* Encoder self-attention alone (MultiHeadAttention.qkv_attention, model.py:276-298):
  * qkv_dev [B, n_audio_ctx, 3 * n_audio_state] (q | k | v per row, cfg.dtype) ->
  * out_dev [B, n_audio_ctx, n_audio_state]; non-causal, scale 1/8.

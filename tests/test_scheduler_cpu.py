@@ -68,7 +68,7 @@ class StubEngine:
 
 
 def _patch_rules_dev(tr):
-    tr._rules_dev = lambda rl: torch.from_numpy(rules_to_array(rl))
+    tr._rules_dev = lambda rl: torch.from_numpy(rl if isinstance(rl, np.ndarray) else rules_to_array(rl))
 
 
 def test_rule_state_machine_pairs_and_budget():
@@ -174,3 +174,43 @@ def test_two_rank_sharding_over_gloo(tmp_path):
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=240)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "GATHERED 7" in out.stdout
+
+
+def test_batch_rule_state_equals_row_state():
+    """The vectorised state used by the scheduler and the per-row reference
+    implementation give the same descriptors and the same bookkeeping on random
+    token streams that follow the rules."""
+    rng = np.random.default_rng(0)
+    n = 16
+    rows = [rules.RowState(max_new=30) for _ in range(n)]
+    bs = rules.BatchRuleState(n, 30)
+    for _ in range(40):
+        act = [i for i in range(n) if not rows[i].done]
+        if not act:
+            break
+        a = rules_to_array([rows[i].rule() for i in act])
+        b = bs.rules_array(act)
+        for r in range(len(act)):
+            ra, rb = a[r].copy(), b[r].copy()
+            assert set(ra[22: 22 + ra[21]]) == set(rb[22: 22 + rb[21]])   # penalty ids as sets
+            ra[21:] = 0
+            rb[21:] = 0
+            assert (ra == rb).all(), (ra, rb)
+        toks = []
+        for r in a:
+            if r[0] >= 0:
+                t = int(r[0])
+            elif r[1] == capi.MODE_ALL_EXCEPT_RANGE:
+                t = TOK_EOT if (r[16] and rng.random() < 0.1) else int(rng.integers(r[2], r[3]))
+            elif r[6] > r[5] and r[6] < 51866 and rng.random() < 0.4:
+                t = int(rng.integers(r[6], 51866))           # a closing timestamp after the opening one
+            else:
+                t = int(rng.integers(0, 50000))
+            toks.append(t)
+        for i, t in zip(act, toks):
+            rows[i].update(t)
+        done = bs.update(act, toks)
+        assert list(done) == [rows[i].done for i in act]
+    assert all(r.done for r in rows)
+    for i in range(n):
+        assert bs.slot_tokens(i) == rows[i].tokens

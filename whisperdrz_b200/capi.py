@@ -63,6 +63,7 @@ SYMBOLS = {
     "wdz_logmel_static": (I, [P, P, I64, P, P, I, P, P]),
     "wdz_encode": (I, [P, P, I, P, P]),
     "wdz_linear": (I, [P, P, I, I, P, P, I, I, P, I, P]),
+    "wdz_linear_rows": (I, [P, P, I, I, P, P, I, I, P, P]),
     "wdz_encoder_attention": (I, [P, P, I, P, I, P]),
     "wdz_cross_kv": (I, [P, P, P, I, P]),
     "wdz_slot_reset": (I, [P, P, I, P]),

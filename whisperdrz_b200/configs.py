@@ -1,0 +1,169 @@
+"""Timings of the other BASELINE.json workloads on one GPU (bench.py times the
+batched end-to-end case):
+
+    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5]
+
+cfg1  one 30 s clip, 4-token prompt, 224 greedy tokens with EOS suppressed (latency; fp32 and bf16)
+cfg2  encoder only, bf16, 16 clips: log-mel + conv stem + 32 layers (time, TFLOP/s)
+cfg3  batched decode, bf16: 32 slots over precomputed cross K/V, prompts U{4..64}, generated U{32..448},
+      forced EOS at the drawn length, timestamp-pair rules (tokens/s)
+cfg5  serving: requests with log-uniform durations 5 s - 10 min and Poisson arrivals, chunks of different
+      requests packed into shared decode steps (throughput, p50/p99 time to final transcript)
+
+Inputs are the seeded synthetic stand-ins of ``synth``; weights are seeded random init.  Prints one JSON
+object per workload."""
+from __future__ import annotations
+
+import json
+import sys
+import time
+
+import numpy as np
+import torch
+
+from . import synth
+from .dims import ModelDimensions, TOK_EOT
+from .engine import Engine
+from .rules import timestamp_tables
+from .transcriber import Transcriber
+from .weights import init_state_dict
+
+ENC_GFLOP_PER_CLIP = 2274.0  # conv 17.7 + 32 x (59.0 GEMM + 11.5 attention)
+
+
+def _timed(fn, reps=3, warm=1):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        out = fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps, out
+
+
+def cfg1(dims, sd):
+    res = {"workload": "cfg1: 1 clip, prompt [sot, en, transcribe, <0.00>], 224 greedy tokens, EOS suppressed"}
+    audio = torch.from_numpy(synth.clips([1])).cuda()
+    for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        e = Engine(dims, sd, dtype=dt, n_slots=2, max_clips=1)
+        rule = e.rules_to_device([{"set_ids": [TOK_EOT]}])
+
+        def run():
+            xa = e.encode(e.logmel(audio))
+            cur = e.rules_argmax(e.prefill(xa, [0], [[50258, 50259, 50360, 50365]]), rule)
+            toks = [cur]
+            for _ in range(223):
+                cur = e.decode_step(cur, [0], rules=rule)
+                toks.append(cur)
+            return torch.cat(toks).tolist()
+        ms, toks = _timed(run, reps=2)
+        res[name] = {"latency_ms": ms, "rtfx": 30000.0 / ms, "tokens": len(toks)}
+        e.close()
+    return res
+
+
+def cfg2(dims, sd):
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=2, max_clips=16)
+    audio = torch.from_numpy(synth.clips(range(1, 17))).cuda()
+    ms_mel, mel = _timed(lambda: e.logmel(audio))
+    ms_enc, _ = _timed(lambda: e.encode(mel))
+    e.close()
+    return {"workload": "cfg2: encoder only, bf16, 16 clips", "logmel_ms": ms_mel, "encoder_ms": ms_enc,
+            "encoder_tflops": 16 * ENC_GFLOP_PER_CLIP / ms_enc, "rtfx_encoder_only": 16 * 30000.0 / (ms_mel + ms_enc)}
+
+
+def cfg3(dims, sd):
+    B = 32
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=B, max_clips=16, max_rows=2048,
+               tables=timestamp_tables(dims.n_vocab))
+    audio = torch.from_numpy(synth.clips(range(1, B + 1))).cuda()
+    for i in range(0, B, 16):
+        e.cross_kv(e.encode(e.logmel(audio[i: i + 16])), list(range(i, i + 16)))
+    p_len, g_len, prompts = synth.decode_lengths(2, B, dims.n_text_ctx)
+
+    def run():
+        tr = Transcriber(e, max_new_tokens=1)   # only its rule state and bookkeeping are used
+        rs = tr.rule_state
+        e.slot_reset(range(B))
+        tok, sl, pos, emit = [], [], [], []
+        for b in range(B):
+            rs.reset(b, int(g_len[b]))
+            for j, t in enumerate(prompts[b]):
+                tok.append(int(t)); sl.append(b); pos.append(j)
+            emit.append(len(tok) - 1)
+        logits = e.forward_rows(tok, sl, pos, emit_rows=emit)
+        ids = list(range(B))
+        cur = e.rules_argmax(logits, tr._rules_dev(rs.rules_array(ids))).tolist()
+        n_tok, steps = 0, 0
+        while ids:
+            done = rs.update(ids, cur)
+            n_tok += len(ids)
+            keep = [i for i, d in zip(range(len(ids)), done) if not d]
+            ids = [ids[i] for i in keep]
+            last = [cur[i] for i in keep]
+            if not ids:
+                break
+            cur = e.decode_step(last, ids, rules=tr._rules_dev(rs.rules_array(ids))).tolist()
+            steps += 1
+        return n_tok, steps
+    ms, (n_tok, steps) = _timed(run, reps=2)
+    e.close()
+    return {"workload": "cfg3: 32 slots, ragged prompts 4-64 and lengths 32-448, forced EOS, timestamp-pair rules",
+            "ms": ms, "tokens": n_tok, "decode_steps": steps, "tokens_per_s": n_tok / ms * 1e3,
+            "prompt_rows": int(p_len.sum()), "mean_generated": float(g_len.mean())}
+
+
+def cfg5(dims, sd, n_req=96, slots=256, seed=4):
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=slots, max_clips=16, tables=timestamp_tables(dims.n_vocab))
+    tr = Transcriber(e, max_new_tokens=224)
+    dur = synth.request_durations(seed, n_req)
+    total_audio = float(dur.sum())
+    rate = 1500.0 / float(dur.mean())          # offered load ~1500x real time: keeps one GPU saturated
+    arrive = synth.poisson_arrivals(seed, n_req, rate)
+    base = synth.long_form(3, 630.0)            # every request is a window of one synthetic recording
+    left, final = {}, {}
+    nxt, t0 = 0, time.perf_counter()
+    while len(final) < n_req:
+        now = time.perf_counter() - t0
+        while nxt < n_req and arrive[nxt] <= now:
+            n = int(dur[nxt] * 16000)
+            a = torch.from_numpy(base[:n])
+            parts = [a[c: c + 480000] for c in range(0, n, 480000)]
+            parts = [p for i, p in enumerate(parts) if i == 0 or len(p) >= 1600]   # drop a sub-0.1 s tail
+            left[nxt] = len(parts)
+            for c, part in enumerate(parts):
+                tr.pending_chunks.append({"audio": part, "id": f"r{nxt}_{c}", "duration": len(part) / 16000,
+                                          "offset": 30.0 * c, "req": nxt})
+            nxt += 1
+        if not tr.busy():
+            time.sleep(max(0.0, min(0.005, arrive[nxt] - now)))
+            continue
+        for res in tr.step():
+            r = res["req"]
+            left[r] -= 1
+            if left[r] == 0:
+                final[r] = time.perf_counter() - t0 - arrive[r]
+    wall = time.perf_counter() - t0
+    lat = np.array(sorted(final.values()))
+    e.close()
+    return {"workload": f"cfg5: {n_req} requests, durations log-uniform 5 s-10 min, Poisson arrivals, {slots} slots",
+            "audio_s": total_audio, "wall_s": wall, "rtfx": total_audio / wall, "offered_rtfx": 1500.0,
+            "p50_s": float(lat[len(lat) // 2]), "p99_s": float(lat[min(len(lat) - 1, int(0.99 * len(lat)))]),
+            "decode_steps": tr.steps, "mean_rows_per_step": tr.launch_rows / max(tr.steps, 1)}
+
+
+def main(argv):
+    want = argv or ["cfg1", "cfg2", "cfg3", "cfg5"]
+    dims = ModelDimensions.from_name("large-v3")
+    sd = init_state_dict(dims, 0)
+    fns = {"cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg5": cfg5}
+    with torch.inference_mode():
+        for w in want:
+            print(json.dumps(fns[w](dims, sd)), flush=True)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

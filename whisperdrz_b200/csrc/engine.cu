@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -91,6 +92,7 @@ struct wdz_engine {
   wdz_rule_desc* g_rules = nullptr;
   struct StepGraph { cudaGraphExec_t exec; long long launches; };
   std::unordered_map<int, StepGraph> step_graphs;
+  int ksplit_override = 0;  // > 0: fixed K split of the residual decode products (tuning experiments)
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
 
   // optional per-kernel timing (wdz_profile): event pairs around selected launches
@@ -587,6 +589,7 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   int ksplit = 1;
   if (epi == EPI_RESID) {
     ksplit = (e->sm_count + tiles - 1) / tiles;
+    if (e->ksplit_override > 0) ksplit = e->ksplit_override;
     if (ksplit > p.kblocks) ksplit = p.kblocks;
     if (ksplit < 1) ksplit = 1;
   }
@@ -658,6 +661,7 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
   wdz_engine* e = new wdz_engine();
   e->cfg = c;
   e->esz = c.dtype == WDZ_BF16 ? 2 : 4;
+  if (const char* ks = getenv("WDZ_KSPLIT")) e->ksplit_override = atoi(ks);
   e->enc.resize(c.n_audio_layer);
   e->dec.resize(c.n_text_layer);
   if (cudaGetDevice(&e->device) == cudaSuccess) {
@@ -843,6 +847,20 @@ int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev
   rc = enc_gemm<bf16>(e, epi, p, st);
   e->cfg.flags = saved;
   return rc;
+}
+
+int wdz_linear_rows(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev, const void* bias_dev, int N,
+                    int accumulate, float* y_dev, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!x_dev || !w_dev || !y_dev || M < 1 || N < 1 || K < 1) return e->fail(WDZ_EINVAL, "wdz_linear_rows: bad argument");
+  cudaStream_t st = (cudaStream_t)s;
+  if (e->cfg.dtype == WDZ_F32)
+    return dec_gemm<float>(e, accumulate ? EPI_RESID : EPI_STORE, (const float*)x_dev, K, w_dev, bias_dev, y_dev, N, M, N,
+                           K, nullptr, st);
+  if (K % 256) return e->fail(WDZ_EINVAL, "wdz_linear_rows: bf16 needs K %% 256 == 0");
+  GemvMmaParams p = mma_params(x_dev, K, w_dev, bias_dev, y_dev, N, M, N, K);
+  return accumulate ? launch_gemv_mma<EPI_RESID, false>(e, p, st) : launch_gemv_mma<EPI_STORE, false>(e, p, st);
 }
 
 int wdz_encoder_attention(wdz_engine* e, const void* qkv_dev, int B, void* out_dev, int cuda_cores_only, wdz_stream s) {

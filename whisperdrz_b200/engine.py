@@ -274,6 +274,21 @@ class Engine:
                                         N, int(gelu), y.data_ptr(), int(cuda_cores_only), self._stream()))
         return y
 
+    def linear_rows(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+        """Decode-shaped product: x [M, K] (engine dtype) @ w[N, K].T (+ bias) -> f32 [M, N];
+        with ``out`` given the result is added into it."""
+        x = x.to(device=self.device, dtype=self.dtype).contiguous()
+        w = w.to(device=self.device, dtype=self.dtype).contiguous()
+        b = None if bias is None else bias.to(device=self.device, dtype=self.dtype).contiguous()
+        M, K = x.shape
+        N = w.shape[0]
+        y = out if out is not None else torch.empty(M, N, dtype=torch.float32, device=self.device)
+        self._check(self.lib.wdz_linear_rows(self.h, x.data_ptr(), M, K, w.data_ptr(),
+                                             None if b is None else b.data_ptr(), N, int(out is not None),
+                                             y.data_ptr(), self._stream()))
+        return y
+
     def encoder_attention(self, qkv: torch.Tensor, cuda_cores_only: bool = False) -> torch.Tensor:
         """qkv [B, n_audio_ctx, 3d] -> [B, n_audio_ctx, d] (non-causal, scale 1/8) in the engine dtype."""
         qkv = qkv.to(device=self.device, dtype=self.dtype).contiguous()

@@ -104,3 +104,96 @@ def segments(tokens: list[int], offset: float = 0.0) -> list[dict]:
         elif t != TOK_EOT and start is not None:
             cur.append(t)
     return out
+
+
+class BatchRuleState:
+    """The state of ``RowState`` for all slots at once, as numpy arrays, so that
+    one decode step builds every active row's descriptor and absorbs every new
+    token without a Python loop over rows (the reference spends its per-step
+    host time in exactly such a loop, decoding.py:1098-1456)."""
+
+    def __init__(self, n_slots: int, max_new: int):
+        import numpy as np
+        self.np = np
+        self.max_new = np.full(n_slots, max_new, np.int64)
+        self.n_new = np.zeros(n_slots, np.int64)
+        self.timing_count = np.zeros(n_slots, np.int64)
+        self.last_timing = np.full(n_slots, -1, np.int64)
+        self.last_was_timing = np.zeros(n_slots, bool)
+        self.recent = np.zeros((n_slots, 10), np.int32)
+        self.n_recent = np.zeros(n_slots, np.int64)
+        self.done = np.zeros(n_slots, bool)
+        self.tokens = np.zeros((n_slots, max_new + 2), np.int32)
+
+    def reset(self, slot: int, max_new: int | None = None) -> None:
+        if max_new is not None:
+            self.max_new[slot] = max_new
+        self.n_new[slot] = self.timing_count[slot] = self.n_recent[slot] = 0
+        self.last_timing[slot] = -1
+        self.last_was_timing[slot] = self.done[slot] = False
+
+    def rules_array(self, idx) -> "np.ndarray":
+        """int32 [len(idx), 32] in ``wdz_rule_desc`` layout for the slots ``idx``."""
+        np = self.np
+        idx = np.asarray(idx, np.int64)
+        n = len(idx)
+        a = np.zeros((n, 32), np.int32)
+        a[:, 0] = -1
+        tc, last, lwt = self.timing_count[idx], self.last_timing[idx], self.last_was_timing[idx]
+        forced = self.n_new[idx] >= self.max_new[idx]
+        first = ~forced & (tc == 0)
+        open_pair = ~forced & (tc % 2 == 1)
+        after_open = open_pair & lwt
+        in_text = open_pair & ~lwt
+        between = ~forced & ~first & ~open_pair
+        forced = forced | (between & (last >= N_TIMINGS - 1))
+        between = between & ~forced
+        a[forced, 0] = TOK_EOT
+        a[first, 1] = capi.MODE_ALL_EXCEPT_RANGE
+        a[first, 2] = TOK_TS_BEGIN
+        a[first, 3] = TOK_TS_BEGIN + FIRST_TIMING_MAX + 1
+        a[after_open, 4] = BIT_SPECIAL | BIT_TIMINGS
+        a[in_text, 4] = BIT_SPECIAL
+        a[in_text, 5] = TOK_TS_BEGIN
+        a[in_text, 6] = (TOK_TS_BEGIN + last + 1)[in_text]
+        lo = TOK_TS_BEGIN + last
+        a[between, 1] = capi.MODE_ALL_EXCEPT_RANGE
+        a[between, 2] = lo[between]
+        a[between, 3] = np.minimum(TOK_TS_END + 1, lo + OPEN_AFTER_CLOSE_SPAN)[between]
+        a[between, 16] = 1
+        a[between, 17] = TOK_EOT
+        pen = open_pair
+        a[pen, 21] = self.n_recent[idx][pen]
+        a[pen, 22:32] = self.recent[idx][pen]
+        return a
+
+    def update(self, idx, toks) -> "np.ndarray":
+        """Absorbs one new token per slot in ``idx``; returns the done flags of those slots."""
+        np = self.np
+        idx = np.asarray(idx, np.int64)
+        toks = np.asarray(toks, np.int64)
+        self.tokens[idx, np.minimum(self.n_new[idx], self.tokens.shape[1] - 1)] = toks
+        self.n_new[idx] += 1
+        end = (toks == TOK_EOT) | (toks < 0)
+        self.done[idx[end]] = True
+        live = ~end
+        is_t = live & (toks >= TOK_TS_BEGIN) & (toks <= TOK_TS_END)
+        it = idx[is_t]
+        self.timing_count[it] += 1
+        self.last_timing[it] = toks[is_t] - TOK_TS_BEGIN
+        self.last_was_timing[it] = True
+        is_w = live & ~is_t
+        iw = idx[is_w]
+        self.last_was_timing[iw] = False
+        full = self.n_recent[iw] >= 10
+        if full.any():
+            f = iw[full]
+            self.recent[f, :9] = self.recent[f, 1:]
+            self.recent[f, 9] = toks[is_w][full]
+        nf = iw[~full]
+        self.recent[nf, self.n_recent[nf]] = toks[is_w][~full]
+        self.n_recent[nf] += 1
+        return self.done[idx]
+
+    def slot_tokens(self, slot: int) -> list[int]:
+        return [int(t) for t in self.tokens[slot, : min(self.n_new[slot], self.tokens.shape[1])]]

@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from .dims import SAMPLE_RATE, TOK_EOT, TOK_LANG_EN, TOK_SOT, TOK_TRANSCRIBE
-from .rules import RowState, segments as token_segments
+from .rules import BatchRuleState, segments as token_segments
 
 
 @dataclass
@@ -40,7 +40,6 @@ class Slot:
     index: int
     status: str = "ready"            # ready -> started -> finished -> ready (transcriber.py:505-509)
     chunk: dict | None = None
-    row: RowState | None = None
     last_token: int = 0
     stop_reason: str = ""
 
@@ -86,6 +85,7 @@ class Transcriber:
         if len(self.init_tokens) + max_new_tokens > engine.max_tokens:
             raise ValueError("prompt + max_new_tokens exceed the KV cache length")
         self.states = [Slot(i) for i in range(self.BS)]
+        self.rule_state = BatchRuleState(self.BS, max_new_tokens)
         self.pending_chunks: list[dict] = []
         self.seconds_processed = 0.0
         self.steps = 0
@@ -136,7 +136,7 @@ class Transcriber:
     def _init_slot(self, slot: Slot, chunk: dict) -> None:
         slot.chunk = chunk
         slot.status = "started"
-        slot.row = RowState(max_new=self.max_new_tokens)
+        self.rule_state.reset(slot.index, self.max_new_tokens)
         slot.stop_reason = ""
 
     def _prefill_slots(self, slots: list[Slot]) -> None:
@@ -172,65 +172,70 @@ class Transcriber:
             xa = eng.encode(mel)
             ids = [s.index for s in grp]
             logits = eng.prefill(xa, ids, [self.init_tokens] * len(grp))
-            rules = [s.row.rule() for s in grp] if self.use_rules else None
-            first_tok = eng.rules_argmax(logits, None if rules is None else self._rules_dev(rules)).tolist()
-            for s, t in zip(grp, first_tok):
-                self._accept(s, int(t))
+            rules = self._rules_dev(self.rule_state.rules_array(ids)) if self.use_rules else None
+            self._accept(grp, eng.rules_argmax(logits, rules).tolist())
 
-    def _rules_dev(self, rules: list[dict]) -> torch.Tensor:
-        a = torch.from_numpy(rules_to_array(rules))
-        return a.to(self.engine.device, non_blocking=False)
+    def _rules_dev(self, rules) -> torch.Tensor:
+        """int32 [n, 32] descriptor array (or a list of rule dicts) -> device tensor."""
+        a = rules if isinstance(rules, np.ndarray) else rules_to_array(rules)
+        return torch.from_numpy(a).to(self.engine.device, non_blocking=False)
 
-    def _accept(self, slot: Slot, tok: int) -> None:
-        slot.row.update(tok)
-        slot.last_token = tok
-        if slot.row.done:
-            slot.status = "finished"
-            slot.stop_reason = "eot" if tok == TOK_EOT else "nan_logits"
-            if slot.row.n_new >= slot.row.max_new:
-                slot.stop_reason = "max_tokens"
+    def _accept(self, slots: list, toks: list) -> None:
+        rs = self.rule_state
+        done = rs.update([s.index for s in slots], toks)
+        for s, t, d in zip(slots, toks, done):
+            s.last_token = int(t)
+            if d:
+                s.status = "finished"
+                s.stop_reason = "eot" if t == TOK_EOT else "nan_logits"
+                if rs.n_new[s.index] > rs.max_new[s.index]:
+                    s.stop_reason = "max_tokens"
 
     def _finish(self, slot: Slot) -> dict:
         c = slot.chunk
-        toks = [t for t in slot.row.tokens if t != TOK_EOT]
+        toks = [t for t in self.rule_state.slot_tokens(slot.index) if t != TOK_EOT]
         res = {k: v for k, v in c.items() if k not in ("audio", "mel")}
         res.update(id=c["id"], tokens=toks, stop_reason=slot.stop_reason,
                    segments=token_segments(toks, c.get("offset", 0.0)))
         if self.text_decoder:
             res["prediction"] = self.text_decoder(toks)
         self.seconds_processed += c.get("duration", 0.0)
-        slot.status, slot.chunk, slot.row = "ready", None, None
+        slot.status, slot.chunk = "ready", None
         return res
 
     @torch.inference_mode()
-    def _run_batched_inference(self):
+    def step(self) -> list[dict]:
+        """One scheduler iteration (the loop body of transcriber.py:1584-1815):
+        refill free slots from ``pending_chunks`` and prefill them, decode one
+        token for every started slot, emit the slots that finished."""
         eng = self.engine
         done: list[dict] = []
-        while True:
-            new = []
-            for s in self.states:
-                if s.status == "ready" and self.pending_chunks:
-                    self._init_slot(s, self.pending_chunks.pop(0))
-                    new.append(s)
-            if new:
-                self._prefill_slots(new)
-            for s in self.states:
-                if s.status == "finished":
-                    done.append(self._finish(s))
-            active = [s for s in self.states if s.status == "started"]
-            if not active:
-                if self.pending_chunks:
-                    continue
-                break
-            rules = self._rules_dev([s.row.rule() for s in active]) if self.use_rules else None
-            nxt = eng.decode_step([s.last_token for s in active], [s.index for s in active], rules=rules)
+        new = []
+        for s in self.states:
+            if s.status == "ready" and self.pending_chunks:
+                self._init_slot(s, self.pending_chunks.pop(0))
+                new.append(s)
+        if new:
+            self._prefill_slots(new)
+        active = [s for s in self.states if s.status == "started"]
+        if active:
+            ids = [s.index for s in active]
+            rules = self._rules_dev(self.rule_state.rules_array(ids)) if self.use_rules else None
+            nxt = eng.decode_step([s.last_token for s in active], ids, rules=rules)
             self.steps += 1
             self.launch_rows += len(active)
-            for s, t in zip(active, nxt.tolist()):
-                self._accept(s, int(t))
-            finished = [s for s in self.states if s.status == "finished"]
-            for s in finished:
+            self._accept(active, nxt.tolist())
+        for s in self.states:
+            if s.status == "finished":
                 done.append(self._finish(s))
-            if finished and not self.pending_chunks and not any(s.status == "started" for s in self.states):
-                break
+        return done
+
+    def busy(self) -> bool:
+        return bool(self.pending_chunks) or any(s.status != "ready" for s in self.states)
+
+    def _run_batched_inference(self):
+        """Drains everything that is pending or in flight (transcriber.py:1532-1829)."""
+        done: list[dict] = []
+        while self.busy():
+            done.extend(self.step())
         return done or None
