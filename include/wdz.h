@@ -54,6 +54,7 @@ typedef struct wdz_config {
 
 #define WDZ_FLAG_NO_TENSOR_CORE 1 /* keep bf16 GEMMs on the CUDA-core path (debug / A-B runs) */
 #define WDZ_FLAG_NO_GRAPH 4       /* launch the decode step kernel by kernel instead of replaying a CUDA graph */
+#define WDZ_FLAG_NO_PDL 8         /* decode kernels launched without programmatic dependent launch */
 #define WDZ_FLAG_NO_BULK_COPY 2   /* cross-attention through plain loads instead of the bulk-copy ring */
 
 /* Per-row logit rule: the device half of decode_batch

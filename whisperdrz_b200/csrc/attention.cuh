@@ -140,6 +140,8 @@ struct AttnDecParams {
 // consumed, so every lane keeps eight 16-byte loads in flight.
 template <typename T>
 __global__ void __launch_bounds__(256) attn_dec_kernel(AttnDecParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int VEC = Vec<T>::N;   // elements per 16-byte piece
   constexpr int LPK = HD / VEC;    // lanes covering one key's head vector
   constexpr int KPI = 32 / LPK;    // keys per warp load
@@ -278,6 +280,8 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
   uint64_t* empty = bars + ATT_STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * ATT_STAGES);
 
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.y, split = blockIdx.x;
   const int slot = p.slots[r];
   int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
@@ -403,6 +407,8 @@ inline size_t attn_dec_stream_smem(int d) {
 // Block = H warps; grid = rows.  Merges the splits that the row's length makes valid.
 template <typename TO>
 __global__ void attn_dec_combine_kernel(AttnDecParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, H = blockDim.x >> 5;
   const int slot = p.slots[r];

@@ -62,6 +62,16 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic
+// stream-serialization attribute may start while its predecessor is still
+// running; pdl_wait() blocks until the predecessor has completed and its
+// writes are visible (a no-op under a normal launch), pdl_trigger() lets the
+// successor begin its own launch.  Every kernel of the decode step calls
+// pdl_wait() before touching global memory, so ordering is preserved while
+// launch latency and prologues overlap.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Device-side error word shared by all kernels of an engine (0 = fine).
 struct DevStatus {
   int code;

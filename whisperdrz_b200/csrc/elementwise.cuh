@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(128)
 layernorm_kernel(const float* __restrict__ x, int64_t ldx, const int* __restrict__ row_idx,
                  const TP* __restrict__ gamma, const TP* __restrict__ beta,
                  TO* __restrict__ y, int64_t ldy, int rows, int d) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int MAXV = 16;  // float4 per lane
   const int r = (blockIdx.x * 128 + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -61,6 +63,8 @@ __global__ void __launch_bounds__(256)
 embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
              const TP* __restrict__ E, const TP* __restrict__ P, float* __restrict__ x,
              int rows, int d, int n_vocab, int n_ctx) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   if (r >= rows) return;
   int t = tokens[r], pos = positions[r];
@@ -73,6 +77,8 @@ embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
 // positions[r] = seq_lens[slot[r]]  (decode step: the next free position of each slot).
 __global__ void positions_from_seqlens_kernel(const int* __restrict__ slots, const int* __restrict__ seq_lens,
                                               int* __restrict__ positions, int n, int n_slots) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= n) return;
   const int s = slots[r];
@@ -82,6 +88,8 @@ __global__ void positions_from_seqlens_kernel(const int* __restrict__ slots, con
 // seq_lens[slot[r]] = max(seq_lens[slot[r]], position[r] + 1)
 __global__ void bump_seqlens_kernel(const int* __restrict__ slots, const int* __restrict__ positions,
                                     int* __restrict__ seq_lens, int n, int n_slots) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= n) return;
   const int s = slots[r];
@@ -100,6 +108,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 kv_append_kernel(const float* __restrict__ qkv, const int* __restrict__ slots, const int* __restrict__ positions,
                  T* __restrict__ cache_k, T* __restrict__ cache_v, int layer, int n_slots, int S, int d, int rows) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   if (r >= rows) return;
   const int s = slots[r], pos = positions[r];

@@ -137,6 +137,20 @@ namespace {
 
 size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
 
+// Launch with the programmatic stream-serialization attribute (kernels that call pdl_wait()).
+template <typename... KArgs, typename... Args>
+void launch_pdl(wdz_engine* e, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (e->cfg.flags & WDZ_FLAG_NO_PDL) ? 0 : 1;
+  cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 int64_t part_entries_for(const wdz_config& c) {
   int64_t a = 8ll * c.max_rows, b = 2048;
   return a > b ? a : b;
@@ -228,11 +242,11 @@ int launch_gemv(wdz_engine* e, const GemvParams& p, cudaStream_t s) {
   // few columns per warp when N is small so that every SM streams weights
   const int warps_needed_1 = p.N;
   if (warps_needed_1 <= 8 * 2 * e->sm_count * 2) {
-    gemv_rows_kernel<T, EPI, 1><<<(p.N + 7) / 8, 256, 0, s>>>(p);
+    launch_pdl(e, gemv_rows_kernel<T, EPI, 1>, dim3((p.N + 7) / 8), dim3(256), 0, s, p);
   } else if (p.N <= 8 * 4 * e->sm_count * 4) {
-    gemv_rows_kernel<T, EPI, 2><<<(p.N + 15) / 16, 256, 0, s>>>(p);
+    launch_pdl(e, gemv_rows_kernel<T, EPI, 2>, dim3((p.N + 15) / 16), dim3(256), 0, s, p);
   } else {
-    gemv_rows_kernel<T, EPI, 4><<<(p.N + 31) / 32, 256, 0, s>>>(p);
+    launch_pdl(e, gemv_rows_kernel<T, EPI, 4>, dim3((p.N + 31) / 32), dim3(256), 0, s, p);
   }
   WDZ_LAUNCH_CHECK(e, "gemv_rows");
   return WDZ_OK;
@@ -265,7 +279,7 @@ template <typename TP, typename TO>
 int launch_ln(wdz_engine* e, const float* x, int64_t ldx, const int* row_idx, const void* g, const void* b,
               TO* y, int64_t ldy, int rows, int d, cudaStream_t s) {
   if (rows <= 0) return WDZ_OK;
-  layernorm_kernel<TP, TO><<<(rows + 3) / 4, 128, 0, s>>>(x, ldx, row_idx, (const TP*)g, (const TP*)b, y, ldy, rows, d);
+  launch_pdl(e, layernorm_kernel<TP, TO>, dim3((rows + 3) / 4), dim3(128), 0, s, x, ldx, row_idx, (const TP*)g, (const TP*)b, y, ldy, rows, d);
   WDZ_LAUNCH_CHECK(e, "layernorm");
   return WDZ_OK;
 }
@@ -355,7 +369,7 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
     // one CTA per SM at a time: pick the split count that fills whole waves best
     int best = 1;
     double best_util = 0.0;
-    for (int c = 1; c <= 24 && (int64_t)rows * c <= e->part_entries && max_len / c >= 32; ++c) {
+    for (int c = 1; c <= (rows <= 4 ? 46 : 24) && (int64_t)rows * c <= e->part_entries && max_len / c >= 32; ++c) {
       const int ctas = rows * c, waves = (ctas + e->sm_count - 1) / e->sm_count;
       const double util = (double)ctas / ((double)waves * e->sm_count);
       if (util > best_util + 0.03) { best_util = util; best = c; }
@@ -376,14 +390,14 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
   const int sp = e->span_begin(cross ? WDZ_PROF_CROSS_ATTN : WDZ_PROF_SELF_ATTN,
                                cross ? 2.0 * rows * max_len * p.d * sizeof(T) : 0.0, s);
   if (stream) {
-    attn_dec_stream_kernel<T><<<dim3(splits, rows), (H + 1) * 32, attn_dec_stream_smem<T>(p.d), s>>>(p, e->status);
+    launch_pdl(e, attn_dec_stream_kernel<T>, dim3(splits, rows), dim3((H + 1) * 32), attn_dec_stream_smem<T>(p.d), s, p, e->status);
   } else {
     int hpc = 1;  // heads per CTA: the largest divisor of H up to 5, so that several CTAs share an SM
     for (int c = 2; c <= 5; ++c) if (H % c == 0) hpc = c;
-    attn_dec_kernel<T><<<dim3(splits, rows, H / hpc), hpc * 32, 0, s>>>(p);
+    launch_pdl(e, attn_dec_kernel<T>, dim3(splits, rows, H / hpc), dim3(hpc * 32), 0, s, p);
   }
   e->span_end(sp, s);
-  attn_dec_combine_kernel<T><<<rows, H * 32, 0, s>>>(p);
+  launch_pdl(e, attn_dec_combine_kernel<T>, dim3(rows), dim3(H * 32), 0, s, p);
   e->launches += 1;
   WDZ_LAUNCH_CHECK(e, "attn_dec");
   return WDZ_OK;
@@ -395,10 +409,22 @@ int launch_gemv_mma(wdz_engine* e, const GemvMmaParams& p, cudaStream_t s) {
   const int sp = e->span_begin(p.W == e->tok_emb ? WDZ_PROF_LM_HEAD : WDZ_PROF_DEC_GEMM, 2.0 * p.N * p.K, s);
   int rc = 1;
 #ifdef WDZ_WITH_TC
-  if (p.M > 16 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) rc = gemm_tc_swap_launch(e, EPI, p, s);
+  if (p.M > 16 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) {
+    // the operand-swapped tcgen05 kernel takes up to 256 rows per launch
+    for (int m0 = 0; m0 < p.M; m0 += 256) {
+      GemvMmaParams q = p;
+      q.M = p.M - m0 < 256 ? p.M - m0 : 256;
+      q.x = p.x + (int64_t)m0 * p.ldx;
+      q.y = OUT_BF16 ? (void*)((bf16*)p.y + (int64_t)m0 * p.ldy) : (void*)((float*)p.y + (int64_t)m0 * p.ldy);
+      if (p.slots) q.slots = p.slots + m0;
+      if (p.positions) q.positions = p.positions + m0;
+      rc = gemm_tc_swap_launch(e, EPI, q, s);
+      if (rc != WDZ_OK) break;   // 1 on the first chunk: shape not taken, nothing launched yet
+    }
+  }
 #endif
   if (rc == 1) {
-    gemv_mma_kernel<EPI, OUT_BF16><<<(p.N + 15) / 16, 256, 0, s>>>(p);
+    launch_pdl(e, gemv_mma_kernel<EPI, OUT_BF16>, dim3((p.N + 15) / 16), dim3(256), 0, s, p);
     e->span_end(sp, s);
     WDZ_LAUNCH_CHECK(e, "gemv_mma");
     return WDZ_OK;
@@ -428,7 +454,7 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
   T* xn = (T*)e->dxn;
   T* ao = (T*)e->dao;
   T* hid = (T*)e->dh;
-  embed_kernel<T><<<n, 256, 0, s>>>(tokens, positions, (const T*)e->tok_emb, (const T*)e->dec_pos, e->dx, n, d,
+  launch_pdl(e, embed_kernel<T>, dim3(n), dim3(256), 0, s, tokens, positions, (const T*)e->tok_emb, (const T*)e->dec_pos, e->dx, n, d,
                                      c.n_vocab, c.n_text_ctx);
   WDZ_LAUNCH_CHECK(e, "embed");
   AttnDecParams ap{};
@@ -436,9 +462,10 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
   ap.part_o = e->part_o; ap.part_ml = e->part_ml; ap.out = ao; ap.ldo = d;
   // y = epi(x W^T + b) with x in T; RESID accumulates into the fp32 residual stream
   auto gemm = [&](int epi, const T* x, int64_t ldx, const void* W, const void* bias, void* y, int64_t ldy, int M,
-                  int N, int K) -> int {
+                  int N, int K, const void* next_w = nullptr, size_t next_bytes = 0) -> int {
     if constexpr (kBf16) {
       GemvMmaParams p = mma_params(x, ldx, W, bias, y, ldy, M, N, K);
+      p.next_w = next_w; p.next_bytes = next_bytes;
       switch (epi) {
         case EPI_STORE: return launch_gemv_mma<EPI_STORE, false>(e, p, s);
         case EPI_RESID: return launch_gemv_mma<EPI_RESID, false>(e, p, s);
@@ -451,16 +478,20 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
   };
   for (int l = 0; l < c.n_text_layer; ++l) {
     const LayerW& w = e->dec[l];
+    const size_t wb = (size_t)d * d * sizeof(T);   // bytes of one d x d weight
+    const void* after = l + 1 < c.n_text_layer ? e->dec[l + 1].qkv_w : e->tok_emb;
+    const size_t after_bytes = l + 1 < c.n_text_layer ? 3 * wb : (size_t)32 << 20;   // a first slice of the LM head
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln1_w, w.ln1_b, xn, d, n, d, s))) return rc;
     if constexpr (kBf16) {
       // fused QKV projection whose epilogue appends K and V to the slot cache
       GemvMmaParams p = mma_params(xn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d);
       p.cache_k = (bf16*)e->self_k; p.cache_v = (bf16*)e->self_v; p.slots = slots; p.positions = positions;
       p.layer = l; p.n_slots = c.n_slots; p.S = c.max_tokens; p.d = d;
+      p.next_w = w.out_w; p.next_bytes = wb;
       if ((rc = launch_gemv_mma<EPI_QKV_CACHE, false>(e, p, s))) return rc;
     } else {
       if ((rc = gemm(EPI_STORE, xn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d))) return rc;
-      kv_append_kernel<T><<<n, 256, 0, s>>>(e->dqkv, slots, positions, (T*)e->self_k, (T*)e->self_v, l, c.n_slots,
+      launch_pdl(e, kv_append_kernel<T>, dim3(n), dim3(256), 0, s, e->dqkv, slots, positions, (T*)e->self_k, (T*)e->self_v, l, c.n_slots,
                                              c.max_tokens, d, n);
       WDZ_LAUNCH_CHECK(e, "kv_append");
     }
@@ -468,20 +499,20 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
     ap.q = e->dqkv; ap.ldq = 3 * d; ap.cache_k = e->self_k; ap.cache_v = e->self_v; ap.S = c.max_tokens;
     ap.positions = positions; ap.fixed_len = 0;
     if ((rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
-    if ((rc = gemm(EPI_RESID, ao, d, w.out_w, w.out_b, e->dx, d, n, d, d))) return rc;
+    if ((rc = gemm(EPI_RESID, ao, d, w.out_w, w.out_b, e->dx, d, n, d, d, w.xq_w, wb))) return rc;
 
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s))) return rc;
-    if ((rc = gemm(EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d))) return rc;
+    if ((rc = gemm(EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, w.xout_w, wb))) return rc;
     ap.q = e->dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
     ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
     if ((rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
-    if ((rc = gemm(EPI_RESID, ao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d))) return rc;
+    if ((rc = gemm(EPI_RESID, ao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d, w.fc1_w, 4 * wb))) return rc;
 
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, xn, d, n, d, s))) return rc;
-    if ((rc = gemm(EPI_GELU, xn, d, w.fc1_w, w.fc1_b, hid, 4 * d, n, 4 * d, d))) return rc;
-    if ((rc = gemm(EPI_RESID, hid, 4 * d, w.fc2_w, w.fc2_b, e->dx, d, n, d, 4 * d))) return rc;
+    if ((rc = gemm(EPI_GELU, xn, d, w.fc1_w, w.fc1_b, hid, 4 * d, n, 4 * d, d, w.fc2_w, 4 * wb))) return rc;
+    if ((rc = gemm(EPI_RESID, hid, 4 * d, w.fc2_w, w.fc2_b, e->dx, d, n, d, 4 * d, after, after_bytes))) return rc;
   }
-  bump_seqlens_kernel<<<(n + 255) / 256, 256, 0, s>>>(slots, positions, e->seq_lens, n, c.n_slots);
+  launch_pdl(e, bump_seqlens_kernel, dim3((n + 255) / 256), dim3(256), 0, s, slots, positions, e->seq_lens, n, c.n_slots);
   WDZ_LAUNCH_CHECK(e, "bump_seqlens");
   // final LayerNorm on the emit rows only, then the tied LM head (model.py:609-613)
   if ((rc = launch_ln<T, T>(e, e->dx, d, emit_rows, e->dec_ln_w, e->dec_ln_b, xn, d, n_emit, d, s))) return rc;
@@ -521,7 +552,7 @@ int rules_launch(wdz_engine* e, const float* logits, const int* row_idx, const w
                  int penalty, int* out, cudaStream_t s) {
   if (n <= 0) return WDZ_OK;
   const int V = e->cfg.n_vocab;
-  rules_argmax_kernel<<<n, 1024, 0, s>>>(logits, V, row_idx, rules, e->tables, (V + 31) / 32, V, penalty, out,
+  launch_pdl(e, rules_argmax_kernel, dim3(n), dim3(1024), 0, s, logits, V, row_idx, rules, e->tables, (V + 31) / 32, V, penalty, out,
                                          e->status);
   WDZ_LAUNCH_CHECK(e, "rules_argmax");
   return WDZ_OK;
@@ -599,6 +630,9 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mpad >> 3) << 17) | ((uint32_t)(tc::BM >> 4) << 24);
   p.cache_k = g.cache_k; p.cache_v = g.cache_v; p.slots = g.slots; p.positions = g.positions;
   p.layer = g.layer; p.n_slots = g.n_slots; p.S = g.S; p.d = g.d;
+  // no L2 prefetch of the next weights here: measured slower at 32-256 rows (it competes with this
+  // kernel's own latency-bound TMA stream); the small-row kernel keeps it
+  p.next_w = nullptr; p.next_bytes = 0;
   p.status = e->status;
   CUtensorMap mw, mx;
   if (!tc::make_map(&mw, g.W, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * g.N, tc::BM, 2))
@@ -606,7 +640,7 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   if (!tc::make_map(&mx, g.x, (uint64_t)g.K, (uint64_t)g.M, 1, (uint64_t)g.ldx * 2, (uint64_t)g.ldx * 2 * g.M,
                     (uint32_t)p.mpad, 2))
     return 1;
-  tc::gemm_tc_swap_kernel<<<dim3(tiles, ksplit), tc::THREADS, tc::SW_SMEM_BYTES, s>>>(mw, mx, p);
+  launch_pdl(e, tc::gemm_tc_swap_kernel, dim3(tiles, ksplit), dim3(tc::THREADS), tc::SW_SMEM_BYTES, s, mw, mx, p);
   WDZ_LAUNCH_CHECK(e, "gemm_tc_swap");
   return WDZ_OK;
 }
@@ -1070,7 +1104,7 @@ int wdz_prefill(wdz_engine* e, const void* xa_dev, const int32_t* window_slot_id
 // lengths, the forward over all rows, logit rules + argmax.
 static int decode_step_body(wdz_engine* e, const int* tokens, const int* slots, const wdz_rule_desc* rules, int n,
                             int* next_out, cudaStream_t st) {
-  positions_from_seqlens_kernel<<<(n + 255) / 256, 256, 0, st>>>(slots, e->seq_lens, e->dpos, n, e->cfg.n_slots);
+  launch_pdl(e, positions_from_seqlens_kernel, dim3((n + 255) / 256), dim3(256), 0, st, slots, e->seq_lens, e->dpos, n, e->cfg.n_slots);
   WDZ_LAUNCH_CHECK(e, "positions");
   int rc = wdz_forward_rows(e, tokens, slots, e->dpos, n, nullptr, n, nullptr, (wdz_stream)st);
   if (rc) return rc;

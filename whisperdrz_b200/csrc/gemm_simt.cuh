@@ -61,6 +61,8 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, int epi, int
 // bias is stored in the weight type TW; outputs of EPI_STORE / EPI_GELU / EPI_CROSS_KV in TO.
 template <typename TA, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256) gemm_tile_kernel(GemmParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int BM = 64, BN = 64, BK = 16, LD = 68;
   __shared__ float As[BK][LD];
   __shared__ float Ws[BK][LD];
@@ -128,6 +130,8 @@ struct GemvParams {
 
 template <typename TW, int EPI, int CPW>
 __global__ void __launch_bounds__(256) gemv_rows_kernel(GemvParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int VEC = Vec<TW>::N;
   constexpr int MT = 8;
   const TW* W = reinterpret_cast<const TW*>(p.W);

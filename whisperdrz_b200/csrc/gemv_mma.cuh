@@ -31,10 +31,24 @@ struct GemvMmaParams {
   // EPI_QKV_CACHE: columns [0, d) -> y (queries, f32 [M, d]); [d, 2d) and [2d, 3d) -> K / V cache rows
   bf16* cache_k; bf16* cache_v; const int* slots; const int* positions;
   int layer, n_slots, S, d;
+  // weights of the product that runs next: pulled into L2 while this one streams its own
+  const void* next_w; size_t next_bytes;
 };
 
+// Each CTA asks L2 for its share of [ptr, ptr + bytes) in 128-byte lines.
+__device__ __forceinline__ void l2_prefetch_share(const void* ptr, size_t bytes, int cta, int n_cta, int tid, int n_thr) {
+  if (!ptr || bytes == 0) return;
+  const size_t lines = (bytes + 127) >> 7;
+  const size_t per = (lines + n_cta - 1) / n_cta;
+  const size_t lo = per * cta, hi = lo + per < lines ? lo + per : lines;
+  const char* base = reinterpret_cast<const char*>(ptr);
+  for (size_t i = lo + tid; i < hi; i += n_thr)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (i << 7)));
+}
+
 constexpr int EPI_QKV_CACHE = 16;
-constexpr int GEMV_MMA_MAXROWS = 64;  // rows per pass (8 MMA n-tiles)
+constexpr int GEMV_MMA_MAXROWS = 16;  // rows per pass (2 MMA n-tiles): keeps registers low, several CTAs per SM
+constexpr int GEMV_MMA_TILES = GEMV_MMA_MAXROWS / 8;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -46,7 +60,9 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 }
 
 template <int EPI, bool OUT_BF16>
-__global__ void __launch_bounds__(256) gemv_mma_kernel(GemvMmaParams p) {
+__global__ void __launch_bounds__(256, 4) gemv_mma_kernel(GemvMmaParams p) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[8][16][GEMV_MMA_MAXROWS + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
@@ -56,25 +72,26 @@ __global__ void __launch_bounds__(256) gemv_mma_kernel(GemvMmaParams p) {
   const int ra = min(n0 + g, p.N - 1), rb = min(n0 + g + 8, p.N - 1);
   const bf16* wa_ptr = p.W + (int64_t)ra * p.K + kbeg + 8 * q;
   const bf16* wb_ptr = p.W + (int64_t)rb * p.K + kbeg + 8 * q;
+  l2_prefetch_share(p.next_w, p.next_bytes, blockIdx.x, gridDim.x, threadIdx.x, 256);
 
   for (int m0 = 0; m0 < p.M; m0 += GEMV_MMA_MAXROWS) {
     const int rows = min(GEMV_MMA_MAXROWS, p.M - m0);
     const int tiles = (rows + 7) >> 3;
-    float acc[8][4];
+    float acc[GEMV_MMA_TILES][4];
 #pragma unroll
-    for (int t = 0; t < 8; ++t)
+    for (int t = 0; t < GEMV_MMA_TILES; ++t)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[t][i] = 0.0f;
-    const bf16* xrow[8];
+    const bf16* xrow[GEMV_MMA_TILES];
 #pragma unroll
-    for (int t = 0; t < 8; ++t) xrow[t] = p.x + (int64_t)min(m0 + t * 8 + g, p.M - 1) * p.ldx + kbeg + 8 * q;
+    for (int t = 0; t < GEMV_MMA_TILES; ++t) xrow[t] = p.x + (int64_t)min(m0 + t * 8 + g, p.M - 1) * p.ldx + kbeg + 8 * q;
 
 #pragma unroll 5
     for (int kb = 0; kb < kslice; kb += 32) {
       const uint4 wa = __ldg(reinterpret_cast<const uint4*>(wa_ptr + kb));
       const uint4 wb = __ldg(reinterpret_cast<const uint4*>(wb_ptr + kb));
 #pragma unroll
-      for (int t = 0; t < 8; ++t) {
+      for (int t = 0; t < GEMV_MMA_TILES; ++t) {
         if (t < tiles) {
           const uint4 xb = *reinterpret_cast<const uint4*>(xrow[t] + kb);
           mma_bf16_16816(acc[t], wa.x, wb.x, wa.y, wb.y, xb.x, xb.y);
@@ -83,7 +100,7 @@ __global__ void __launch_bounds__(256) gemv_mma_kernel(GemvMmaParams p) {
       }
     }
 #pragma unroll
-    for (int t = 0; t < 8; ++t) {
+    for (int t = 0; t < GEMV_MMA_TILES; ++t) {
       if (t < tiles) {
         red[warp][g][t * 8 + 2 * q] = acc[t][0];
         red[warp][g][t * 8 + 2 * q + 1] = acc[t][1];

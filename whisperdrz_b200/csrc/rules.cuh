@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(1024)
 rules_argmax_kernel(const float* __restrict__ logits, int64_t ld, const int* __restrict__ row_idx,
                     const wdz_rule_desc* __restrict__ rules, const uint32_t* __restrict__ tables,
                     int words, int V, int apply_penalty, int* __restrict__ out, DevStatus* status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ wdz_rule_desc rd;
   __shared__ float best_v[32];
   __shared__ int best_i[32];
