@@ -370,3 +370,25 @@ def test_drop_in_model_follows_the_reference_call_sequence(golden_dir):
     assert np.array_equal(torch.stack(toks, 1).numpy(), g["tokens"])
     assert np.array_equal(self_kv[0].seq_lens.cpu().numpy()[1: B + 1], g["final_seq_lens"][1: B + 1])
     m.engine.close()
+
+
+def test_rules_kernel_matches_reference_decode_batch(golden_dir):
+    """The device rule kernel on the cases recorded from the reference's own
+    decode_batch (tests/golden/make_rules_golden.py): identical token ids for
+    Phase 3 (with penalty) and Phase 4 (re-argmax, no penalty)."""
+    from test_oracle_golden import _rules_cases
+    from whisperdrz_b200.engine import Engine
+    cases = _rules_cases(golden_dir)
+    dims = ModelDimensions.from_name("test-small")
+    sd = init_state_dict(dims, 0)
+    for lo in range(0, len(cases), 32):
+        part = cases[lo: lo + 32]
+        tables = torch.stack([c[1] for c in part])
+        e = Engine(dims, sd, dtype=torch.float32, n_slots=2, max_clips=1, tables=tables)
+        logits = torch.stack([c[0] for c in part]).cuda()
+        rules = [{"table_bits": 1 << i, "pen_ids": c[2]} for i, c in enumerate(part)]
+        with_pen = e.rules_argmax(logits, rules, penalty=True).cpu().tolist()
+        no_pen = e.rules_argmax(logits, rules, penalty=False).cpu().tolist()
+        for i, c in enumerate(part):
+            assert (with_pen[i] if c[3] == 3 else no_pen[i]) == c[4], (lo + i, c[3])
+        e.close()

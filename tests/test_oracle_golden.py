@@ -94,3 +94,28 @@ def test_rules_argmax_semantics():
     assert oracle.rules_argmax(lg, [{}], tables)[0] == 5
     assert oracle.rules_argmax(lg, [{"pen_ids": [5]}], tables)[0] == 9
     assert oracle.rules_argmax(lg, [{"pen_ids": [5]}], tables, penalty=False)[0] == 5
+
+
+def _rules_cases(golden_dir):
+    g = np.load(os.path.join(golden_dir, "rules_phase34.npz"))
+    V = 51866
+    cases = []
+    for i in range(len(g["seed"])):
+        gen = torch.Generator().manual_seed(int(g["seed"][i]))
+        lg = torch.randn(int(g["rows"][i]), V, generator=gen) * float(g["scale"])
+        mask = torch.from_numpy(np.unpackbits(g["mask"][i], bitorder="little")[:V].astype(bool))
+        pen = [int(t) for t in g["pen"][i] if t >= 0]
+        cases.append((lg[int(g["row"][i])], mask, pen, int(g["phase"][i]), int(g["token"][i])))
+    return cases
+
+
+def test_rules_argmax_matches_reference_decode_batch(golden_dir):
+    """Phase 3 (mask + repetition penalty + argmax) and Phase 4 (re-argmax under
+    a new mask, no penalty) of the reference's decode_batch, recorded by
+    tests/golden/make_rules_golden.py: same logits, same blocked set, same
+    penalised ids -> same token id."""
+    cases = _rules_cases(golden_dir)
+    assert len(cases) >= 30 and any(c[3] == 4 for c in cases) and any(c[2] for c in cases)
+    for lg, mask, pen, phase, tok in cases:
+        got = oracle.rules_argmax(lg[None], [{"table_bits": 1, "pen_ids": pen}], mask[None], penalty=phase == 3)
+        assert int(got[0]) == tok
