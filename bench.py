@@ -176,7 +176,7 @@ def main():
     audio_dev = audio_host.to(dev)
 
     def one_step(src):
-        tr = Transcriber(eng, max_new_tokens=args.new_tokens)
+        tr = Transcriber(eng, max_new_tokens=args.new_tokens, max_continuations=0)
         for i in range(args.clips):
             tr.pending_chunks.append({"audio": src[i], "id": f"chunk_{i}", "duration": 30.0, "offset": 0.0})
         out = []

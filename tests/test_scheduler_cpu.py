@@ -22,14 +22,17 @@ class StubEngine:
     descriptors the way the device kernel does (forced id, allowed range)."""
     n_slots, max_tokens, max_clips = 4, 448, 2
     device = torch.device("cpu")
+    emit_eot = True
 
     def __init__(self):
         self.calls = {"logmel": 0, "encode": 0, "prefill": 0, "decode": 0}
         self.rows_per_step = []
+        self.offsets = []
         self.count = {}
 
-    def logmel(self, buf, n_samples=None):
+    def logmel(self, buf, n_samples=None, frame_offset=None):
         self.calls["logmel"] += 1
+        self.offsets.append(frame_offset)
         assert buf.shape[0] <= self.max_clips and buf.shape[1] == 480000
         return torch.zeros(buf.shape[0], 128, 3000)
 
@@ -49,7 +52,7 @@ class StubEngine:
             return r[0]
         self.count[slot] += 1
         if r[1] == capi.MODE_ALL_EXCEPT_RANGE:
-            if r[16] and self.count[slot] % 7 == 0:
+            if self.emit_eot and r[16] and self.count[slot] % 7 == 0:
                 return TOK_EOT                       # cleared id: EOT allowed between pairs
             return min(r[2] + 3, r[3] - 1)
         if r[6] > r[5] and self.count[slot] % 3 == 0:
@@ -104,7 +107,7 @@ def test_rules_to_array_layout():
 
 def test_scheduler_continuous_batching_with_stub_engine():
     eng = StubEngine()
-    tr = Transcriber(eng, max_new_tokens=40)
+    tr = Transcriber(eng, max_new_tokens=40, max_continuations=0)
     _patch_rules_dev(tr)
     audio = torch.randn(int(16000 * 30 * 9.5))       # 10 chunks for 4 slots
     res = tr.transcribe(audio)
@@ -214,3 +217,29 @@ def test_batch_rule_state_equals_row_state():
     assert all(r.done for r in rows)
     for i in range(n):
         assert bs.slot_tokens(i) == rows[i].tokens
+
+
+def test_continuation_windows_restart_at_the_last_closing_timestamp():
+    """A window that hits its token budget before the end of its chunk is
+    continued from its last closing timestamp (reference: transcriber.py:1283-1334):
+    the kept tokens end on a closing timestamp, the next window's mel starts at
+    that offset, segments stay monotonic, and the cap on continuations holds."""
+    eng = StubEngine()
+    eng.emit_eot = False                              # windows end only by running out of tokens
+    tr = Transcriber(eng, max_new_tokens=12, max_continuations=3)
+    _patch_rules_dev(tr)
+    res = tr.transcribe(torch.randn(16000 * 30))
+    r = res.raw_chunks[0]
+    assert r["windows"] == 4 and r["stop_reason"] == "max_tokens"       # 1 + 3 continuations, then emitted
+    offs = [o[0] for o in eng.offsets if o is not None]
+    assert len(offs) == 3 and offs == sorted(offs) and offs[0] >= 100   # each window starts >= 1 s later
+    starts = [s["start"] for s in r["segments"]]
+    assert starts == sorted(starts) and all(s["end"] > s["start"] for s in r["segments"])
+    # every kept window contributes an even number of timestamps (closed pairs only)
+    n_ts = sum(1 for t in r["tokens"] if t >= TOK_TS_BEGIN)
+    assert n_ts >= 2 * len(r["segments"]) - 1
+    eng0 = StubEngine()
+    eng0.emit_eot = False
+    tr0 = Transcriber(eng0, max_new_tokens=12, max_continuations=0)
+    _patch_rules_dev(tr0)
+    assert tr0.transcribe(torch.randn(16000 * 30)).raw_chunks[0]["windows"] == 1

@@ -118,7 +118,7 @@ def cfg3(dims, sd):
 
 def cfg5(dims, sd, n_req=96, slots=256, seed=4):
     e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=slots, max_clips=16, tables=timestamp_tables(dims.n_vocab))
-    tr = Transcriber(e, max_new_tokens=224)
+    tr = Transcriber(e, max_new_tokens=224, max_continuations=0)
     dur = synth.request_durations(seed, n_req)
     total_audio = float(dur.sum())
     rate = 1500.0 / float(dur.mean())          # offered load ~1500x real time: keeps one GPU saturated

@@ -42,6 +42,10 @@ class Slot:
     chunk: dict | None = None
     last_token: int = 0
     stop_reason: str = ""
+    win_offset: float = 0.0          # start of the current window inside the chunk, seconds
+    continuations: int = 0
+    kept_tokens: list = field(default_factory=list)     # tokens of earlier windows of this chunk
+    kept_segments: list = field(default_factory=list)
 
 
 def rules_to_array(rules: list[dict]) -> np.ndarray:
@@ -68,11 +72,14 @@ def rules_to_array(rules: list[dict]) -> np.ndarray:
 class Transcriber:
     def __init__(self, engine, BS: int | None = None, max_audio_length: float = 30.0,
                  max_new_tokens: int = 224, lang: str | None = "en", use_rules: bool = True,
-                 text_decoder=None):
+                 text_decoder=None, max_continuations: int = 20):
         """engine: ``whisperdrz_b200.engine.Engine`` (or an object with the same
         methods).  BS: concurrent slots, at most the engine's.  max_new_tokens:
         generated tokens per 30 s window before EOT is forced.  text_decoder:
-        optional ``list[int] -> str`` (the tokenizer is not part of this path)."""
+        optional ``list[int] -> str`` (the tokenizer is not part of this path).
+        max_continuations: a window that ran out of tokens before the end of its
+        chunk is continued from its last closing timestamp, at most this many
+        times (transcriber.py:1283-1334; 0 disables)."""
         self.engine = engine
         self.BS = BS or engine.n_slots
         if self.BS > engine.n_slots:
@@ -81,6 +88,7 @@ class Transcriber:
         self.max_new_tokens = max_new_tokens
         self.use_rules = use_rules
         self.text_decoder = text_decoder
+        self.max_continuations = max_continuations
         self.init_tokens = [TOK_SOT, TOK_LANG_EN, TOK_TRANSCRIBE] if lang else [TOK_SOT]
         if len(self.init_tokens) + max_new_tokens > engine.max_tokens:
             raise ValueError("prompt + max_new_tokens exceed the KV cache length")
@@ -138,6 +146,8 @@ class Transcriber:
         slot.status = "started"
         self.rule_state.reset(slot.index, self.max_new_tokens)
         slot.stop_reason = ""
+        slot.win_offset, slot.continuations = 0.0, 0
+        slot.kept_tokens, slot.kept_segments = [], []
 
     def _prefill_slots(self, slots: list[Slot]) -> None:
         """Log-mel + encoder + cross K/V + prompt for new slots, then their first token."""
@@ -168,7 +178,10 @@ class Transcriber:
                     host[i, : n[i]] = torch.as_tensor(s.chunk["audio"][: n[i]], dtype=torch.float32)
                     host[i, n[i]:] = 0.0
                 buf = host.to(dev, non_blocking=True)
-            mel = eng.logmel(buf, n_samples=n)
+            # a continuation window starts at its offset inside the chunk; the (max - 8) floor is still
+            # taken over the whole chunk (transcriber.py:1062-1072)
+            offs = [int(round(s.win_offset * 100)) for s in grp]
+            mel = eng.logmel(buf, n_samples=n, frame_offset=offs if any(offs) else None)
             xa = eng.encode(mel)
             ids = [s.index for s in grp]
             logits = eng.prefill(xa, ids, [self.init_tokens] * len(grp))
@@ -191,16 +204,42 @@ class Transcriber:
                 if rs.n_new[s.index] > rs.max_new[s.index]:
                     s.stop_reason = "max_tokens"
 
-    def _finish(self, slot: Slot) -> dict:
+    def _finish(self, slot: Slot) -> dict | None:
+        """Emits a finished slot, or turns it into a continuation window (returns None)."""
         c = slot.chunk
         toks = [t for t in self.rule_state.slot_tokens(slot.index) if t != TOK_EOT]
+        base = c.get("offset", 0.0) + slot.win_offset
+        segs = token_segments(toks, base)
+        duration = c.get("duration", 0.0)
+        if (slot.stop_reason == "max_tokens" and slot.continuations < self.max_continuations and segs
+                and duration - (segs[-1]["end"] - c.get("offset", 0.0)) > 0.5):
+            # out of tokens before the end of the chunk: keep everything up to the last closing
+            # timestamp and decode a new window that starts there (at least 1 s further on)
+            last_end = segs[-1]["end"] - base
+            n_keep = 0
+            closes = 0
+            for i, t in enumerate(toks):
+                if t >= 50365:
+                    closes += 1
+                    if closes == 2 * len(segs):
+                        n_keep = i + 1
+                        break
+            slot.kept_tokens += toks[:n_keep]
+            slot.kept_segments += segs
+            slot.win_offset += max(last_end, 1.0)
+            slot.continuations += 1
+            self.rule_state.reset(slot.index, self.max_new_tokens)
+            slot.status, slot.stop_reason = "continue", ""
+            return None
+        all_toks = slot.kept_tokens + toks
         res = {k: v for k, v in c.items() if k not in ("audio", "mel")}
-        res.update(id=c["id"], tokens=toks, stop_reason=slot.stop_reason,
-                   segments=token_segments(toks, c.get("offset", 0.0)))
+        res.update(id=c["id"], tokens=all_toks, stop_reason=slot.stop_reason, windows=slot.continuations + 1,
+                   segments=slot.kept_segments + segs)
         if self.text_decoder:
-            res["prediction"] = self.text_decoder(toks)
-        self.seconds_processed += c.get("duration", 0.0)
+            res["prediction"] = self.text_decoder(all_toks)
+        self.seconds_processed += duration
         slot.status, slot.chunk = "ready", None
+        slot.kept_tokens, slot.kept_segments = [], []
         return res
 
     @torch.inference_mode()
@@ -212,7 +251,10 @@ class Transcriber:
         done: list[dict] = []
         new = []
         for s in self.states:
-            if s.status == "ready" and self.pending_chunks:
+            if s.status == "continue":
+                s.status = "started"
+                new.append(s)
+            elif s.status == "ready" and self.pending_chunks:
                 self._init_slot(s, self.pending_chunks.pop(0))
                 new.append(s)
         if new:
@@ -227,7 +269,9 @@ class Transcriber:
             self._accept(active, nxt.tolist())
         for s in self.states:
             if s.status == "finished":
-                done.append(self._finish(s))
+                r = self._finish(s)
+                if r is not None:
+                    done.append(r)
         return done
 
     def busy(self) -> bool:
