@@ -392,3 +392,31 @@ def test_rules_kernel_matches_reference_decode_batch(golden_dir):
         for i, c in enumerate(part):
             assert (with_pen[i] if c[3] == 3 else no_pen[i]) == c[4], (lo + i, c[3])
         e.close()
+
+
+def test_transcribe_end_to_end_identical_to_oracle_scheduler():
+    """The whole path behind ``Transcriber.transcribe`` - chunking, slot refill,
+    log-mel, encoder, prefill, rule-constrained greedy decode, a continuation
+    window, stitching - on the fp32 CUDA engine against the same scheduler
+    driven by the CPU oracle: identical tokens, segments and stop reasons."""
+    from oracle_engine import OracleEngine
+    from whisperdrz_b200.engine import Engine
+    from whisperdrz_b200.rules import timestamp_tables
+    from whisperdrz_b200.transcriber import Transcriber
+    dims = ModelDimensions.from_name("test-small")
+    sd = init_state_dict(dims, 0)
+    audio = torch.from_numpy(synth.long_form(5, 71.0))           # 3 chunks, the last one 11 s
+    kw = dict(max_new_tokens=20, max_continuations=1)
+    ref_tr = Transcriber(OracleEngine(dims, sd, n_slots=2, max_clips=2), **kw)
+    ref_tr._rules_dev = lambda a: torch.from_numpy(a)
+    want = ref_tr.transcribe(audio)
+    e = Engine(dims, sd, dtype=torch.float32, n_slots=2, max_clips=2, tables=timestamp_tables(dims.n_vocab))
+    got = Transcriber(e, **kw).transcribe(audio)
+    e.device_status()
+    assert [r["id"] for r in got.raw_chunks] == ["chunk_0", "chunk_1", "chunk_2"]
+    for a, b in zip(got.raw_chunks, want.raw_chunks):
+        assert a["tokens"] == b["tokens"]
+        assert a["stop_reason"] == b["stop_reason"] and a["windows"] == b["windows"]
+    assert got.segments == want.segments and len(got.segments) >= 3
+    assert any(r["windows"] == 2 for r in got.raw_chunks)        # the continuation path ran
+    e.close()
