@@ -53,6 +53,41 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// tcgen05.ld without the wait, so that two loads share one round trip.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+// Waits for the loads above; the registers pass through the statement so that no use can move ahead of it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[32], uint32_t (&b)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) asm volatile("" : "+r"(a[i]), "+r"(b[i]));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+
 __global__ void __launch_bounds__(192, 2)
 attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -145,47 +180,76 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
       if (!ok) break;
       tc_fence_after();
       const int k0 = j * KT;
+      const bool tail = k0 + KT > p.T;          // only the last key tile has columns past the sequence
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(lane_addr + COL_S + c * 32, v);
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t a[32], b[32];
+        tmem_ld32_issue(lane_addr + COL_S + hf * 64, a);
+        tmem_ld32_issue(lane_addr + COL_S + hf * 64 + 32, b);
+        tmem_ld_wait(a, b);
+        if (!tail) {
+          // four independent chains instead of one 64-long dependent chain
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (k0 + c * 32 + i < p.T) mx = fmaxf(mx, v[i]);
+          for (int i = 0; i < 32; i += 2) {
+            m0 = fmaxf(m0, __uint_as_float(a[i])); m1 = fmaxf(m1, __uint_as_float(a[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(b[i])); m3 = fmaxf(m3, __uint_as_float(b[i + 1]));
+          }
+          mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (k0 + hf * 64 + i < p.T) mx = fmaxf(mx, __uint_as_float(a[i]));
+            if (k0 + hf * 64 + 32 + i < p.T) mx = fmaxf(mx, __uint_as_float(b[i]));
+          }
+        }
       }
       const float m_new = fmaxf(m, mx * QK_SCALE_LOG2E);
-      const float alpha = exp2f(m - m_new);
+      const float alpha = ex2(m - m_new);
       if (j > 0) {
         ok = mbar_wait(pv_full, (j - 1) & 1, abort_flag, p.status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        uint32_t a[32], b[32];
+        tmem_ld32_issue(lane_addr + COL_O, a);
+        tmem_ld32_issue(lane_addr + COL_O + 32, b);
+        tmem_ld_wait(a, b);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float v[32];
-          tmem_ld32(lane_addr + COL_O + c * 32, v);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + v[i]) * alpha;
+        for (int i = 0; i < 32; ++i) {
+          o[i] = (o[i] + __uint_as_float(a[i])) * alpha;
+          o[32 + i] = (o[32 + i] + __uint_as_float(b[i])) * alpha;
         }
       }
-      float sum = 0.0f;
+      float sum = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(lane_addr + COL_S + c * 32, v);
-        uint32_t pk[16];
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t a[32], b[32], pk[32];
+        tmem_ld32_issue(lane_addr + COL_S + hf * 64, a);
+        tmem_ld32_issue(lane_addr + COL_S + hf * 64 + 32, b);
+        tmem_ld_wait(a, b);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int kk = k0 + c * 32 + 2 * i;
-          const float p0 = kk < p.T ? exp2f(v[2 * i] * QK_SCALE_LOG2E - m_new) : 0.0f;
-          const float p1 = kk + 1 < p.T ? exp2f(v[2 * i + 1] * QK_SCALE_LOG2E - m_new) : 0.0f;
-          sum += p0 + p1;
+          float p0 = ex2(fmaf(__uint_as_float(a[2 * i]), QK_SCALE_LOG2E, -m_new));
+          float p1 = ex2(fmaf(__uint_as_float(a[2 * i + 1]), QK_SCALE_LOG2E, -m_new));
+          float p2 = ex2(fmaf(__uint_as_float(b[2 * i]), QK_SCALE_LOG2E, -m_new));
+          float p3 = ex2(fmaf(__uint_as_float(b[2 * i + 1]), QK_SCALE_LOG2E, -m_new));
+          if (tail) {
+            const int kk = k0 + hf * 64 + 2 * i;
+            if (kk >= p.T) p0 = 0.0f;
+            if (kk + 1 >= p.T) p1 = 0.0f;
+            if (kk + 32 >= p.T) p2 = 0.0f;
+            if (kk + 33 >= p.T) p3 = 0.0f;
+          }
+          sum += p0; sum1 += p1; sum2 += p2; sum3 += p3;
           pk[i] = pack_bf16(p0, p1);
+          pk[16 + i] = pack_bf16(p2, p3);
         }
-        tmem_st16(lane_addr + COL_P + c * 16, pk);
+        tmem_st32(lane_addr + COL_P + hf * 32, pk);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      sum = (sum + sum1) + (sum2 + sum3);
       l = l * alpha + sum;
       m = m_new;
       tc_fence_before();
