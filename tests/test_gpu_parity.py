@@ -420,3 +420,23 @@ def test_transcribe_end_to_end_identical_to_oracle_scheduler():
     assert got.segments == want.segments and len(got.segments) >= 3
     assert any(r["windows"] == 2 for r in got.raw_chunks)        # the continuation path ran
     e.close()
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 40, 256, 300])
+def test_decode_shaped_linear_matches_fp32_reference(small_bf16, M):
+    """wdz_linear_rows: the mma.sync weight-streaming kernel (<= 16 rows) and the
+    operand-swapped tcgen05 kernel (more rows, chunked above 256) against an fp32
+    product of the same bf16 operands, storing and accumulating."""
+    e, _, _ = small_bf16
+    g = torch.Generator().manual_seed(M)
+    N, K = 1280, 1024
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
+    b = (torch.randn(N, generator=g) * 0.1).bfloat16()
+    ref = x.float() @ w.float().T + b.float()
+    got = e.linear_rows(x, w, b).cpu()
+    assert (got - ref).abs().max() / ref.abs().max() < 2e-5
+    acc = torch.full((M, N), 0.5, device="cuda")
+    e.linear_rows(x, w, b, out=acc)
+    assert (acc.cpu() - (ref + 0.5)).abs().max() / ref.abs().max() < 2e-5
+    e.device_status()

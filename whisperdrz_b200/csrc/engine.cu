@@ -92,6 +92,7 @@ struct wdz_engine {
   wdz_rule_desc* g_rules = nullptr;
   struct StepGraph { cudaGraphExec_t exec; long long launches; };
   std::unordered_map<int, StepGraph> step_graphs;
+  int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
   int ksplit_override = 0;  // > 0: fixed K split of the residual decode products (tuning experiments)
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
 
@@ -409,7 +410,7 @@ int launch_gemv_mma(wdz_engine* e, const GemvMmaParams& p, cudaStream_t s) {
   const int sp = e->span_begin(p.W == e->tok_emb ? WDZ_PROF_LM_HEAD : WDZ_PROF_DEC_GEMM, 2.0 * p.N * p.K, s);
   int rc = 1;
 #ifdef WDZ_WITH_TC
-  if (p.M > 16 && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) {
+  if (p.M > e->gemv_max_rows && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) {
     // the operand-swapped tcgen05 kernel takes up to 256 rows per launch
     for (int m0 = 0; m0 < p.M; m0 += 256) {
       GemvMmaParams q = p;
@@ -696,6 +697,7 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
   e->cfg = c;
   e->esz = c.dtype == WDZ_BF16 ? 2 : 4;
   if (const char* ks = getenv("WDZ_KSPLIT")) e->ksplit_override = atoi(ks);
+  if (const char* gm = getenv("WDZ_GEMV_MAX_ROWS")) e->gemv_max_rows = atoi(gm);
   e->enc.resize(c.n_audio_layer);
   e->dec.resize(c.n_text_layer);
   if (cudaGetDevice(&e->device) == cudaSuccess) {
