@@ -148,6 +148,9 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=224)
     ap.add_argument("--cpu-decode-steps", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--host-rules", action="store_true", help="rule state on the host, one decode step per round trip")
+    ap.add_argument("--steps-per-poll", type=int, default=8)
+    ap.add_argument("--engine-flags", type=int, default=0, help="WDZ_FLAG_* bits (A/B runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -171,12 +174,14 @@ def main():
     dims = ModelDimensions.from_name(args.model)
     sd = init_state_dict(dims, 0)
     eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(16, args.clips),
+                 flags=args.engine_flags,
                  tables=timestamp_tables(dims.n_vocab))
     audio_host = torch.from_numpy(synth.clips([1000 * rank + i + 1 for i in range(args.clips)])).pin_memory()
     audio_dev = audio_host.to(dev)
 
     def one_step(src):
-        tr = Transcriber(eng, max_new_tokens=args.new_tokens, max_continuations=0)
+        tr = Transcriber(eng, max_new_tokens=args.new_tokens, max_continuations=0,
+                         device_rules=not args.host_rules, steps_per_poll=args.steps_per_poll)
         for i in range(args.clips):
             tr.pending_chunks.append({"audio": src[i], "id": f"chunk_{i}", "duration": 30.0, "offset": 0.0})
         out = []

@@ -217,6 +217,31 @@ int wdz_prefill(wdz_engine* e, const void* xa_dev, const int32_t* window_slot_id
 int wdz_decode_step(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slot_ids_dev, int n_active,
                     const wdz_rule_desc* rules_dev, int32_t* next_tokens_out_dev,
                     float* logits_out_dev, wdz_stream s);
+/* ---- decode with the token-level rule state on the device --------------------
+ * The timestamp-pair rules (timestamps in open/close pairs, never backwards,
+ * first one early, specials never sampled, EOT only between pairs, repetition
+ * penalty on the last ten text tokens, forced EOT at the budget: the part of
+ * decode_batch / update_state_after_decode, decoding.py:878-963 and 1098-1777,
+ * that needs no text) depend on a few integers per slot.  Kept on the device
+ * they remove the reference's per-step host round trip: k decode steps are
+ * queued by one call and the host only polls.  Class table 0 must hold the
+ * special tokens and table 1 the timestamp tokens (or pass other bits to
+ * wdz_ts_configure; defaults are the multilingual ids 50257 / 50365..51865). */
+int wdz_ts_configure(wdz_engine* e, int eot, int ts_begin, int ts_end, int first_timing_max,
+                     int open_after_close_span, uint32_t bit_special, uint32_t bit_timings);
+/* Fresh state for the given slots; max_new_dev int32 [n] = token budget of each (EOT is forced at it). */
+int wdz_ts_reset(wdz_engine* e, const int32_t* slot_ids_dev, const int32_t* max_new_dev, int n, wdz_stream s);
+/* First token after a prefill: logits_dev f32 [n, n_vocab] of the last prompt position of each slot. */
+int wdz_ts_first(wdz_engine* e, const float* logits_dev, const int32_t* slot_ids_dev, int n, wdz_stream s);
+/* k decode steps for the n slots: each step feeds every slot its last token, applies its rule, argmax,
+ * updates its state and appends the token to its log.  Finished slots keep producing EOT until dropped. */
+int wdz_ts_steps(wdz_engine* e, const int32_t* slot_ids_dev, int n, int k, wdz_stream s);
+/* Copies all slot states to host (24 x int32 per slot: max_new, n_new, timing_count, last_timing,
+ * last_was_timing, n_recent, done, last_token, recent[10], 6 spare).  Synchronises the stream. */
+int wdz_ts_poll(wdz_engine* e, int32_t* out_host, wdz_stream s);
+/* Copies the first cap generated tokens of one slot to host.  Synchronises the stream. */
+int wdz_ts_tokens(wdz_engine* e, int slot, int32_t* out_host, int cap, wdz_stream s);
+
 /* Phase-4 re-argmax (decoding.py:2033-2044, _sample_masked :2049-2067) on the
  * logits of the last wdz_decode_step / wdz_forward_rows: rows_dev[i] indexes
  * that call's logit rows; no repetition penalty. */

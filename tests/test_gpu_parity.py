@@ -411,14 +411,16 @@ def test_transcribe_end_to_end_identical_to_oracle_scheduler():
     ref_tr._rules_dev = lambda a: torch.from_numpy(a)
     want = ref_tr.transcribe(audio)
     e = Engine(dims, sd, dtype=torch.float32, n_slots=2, max_clips=2, tables=timestamp_tables(dims.n_vocab))
-    got = Transcriber(e, **kw).transcribe(audio)
-    e.device_status()
-    assert [r["id"] for r in got.raw_chunks] == ["chunk_0", "chunk_1", "chunk_2"]
-    for a, b in zip(got.raw_chunks, want.raw_chunks):
-        assert a["tokens"] == b["tokens"]
-        assert a["stop_reason"] == b["stop_reason"] and a["windows"] == b["windows"]
-    assert got.segments == want.segments and len(got.segments) >= 3
-    assert any(r["windows"] == 2 for r in got.raw_chunks)        # the continuation path ran
+    # rule state on the device (several steps per host round trip) and on the host (one step per round trip)
+    for mode in (dict(device_rules=True, steps_per_poll=5), dict(device_rules=False)):
+        got = Transcriber(e, **kw, **mode).transcribe(audio)
+        e.device_status()
+        assert [r["id"] for r in got.raw_chunks] == ["chunk_0", "chunk_1", "chunk_2"]
+        for a, b in zip(got.raw_chunks, want.raw_chunks):
+            assert a["tokens"] == b["tokens"], mode
+            assert a["stop_reason"] == b["stop_reason"] and a["windows"] == b["windows"]
+        assert got.segments == want.segments and len(got.segments) >= 3
+        assert any(r["windows"] == 2 for r in got.raw_chunks)    # the continuation path ran
     e.close()
 
 

@@ -72,6 +72,12 @@ SYMBOLS = {
     "wdz_forward_rows": (I, [P, P, P, P, I, P, I, P, P]),
     "wdz_prefill": (I, [P, P, P, I, P, P, P, I, P, I, P, P]),
     "wdz_decode_step": (I, [P, P, P, I, P, P, P, P]),
+    "wdz_ts_configure": (I, [P, I, I, I, I, I, C.c_uint32, C.c_uint32]),
+    "wdz_ts_reset": (I, [P, P, P, I, P]),
+    "wdz_ts_first": (I, [P, P, P, I, P]),
+    "wdz_ts_steps": (I, [P, P, I, I, P]),
+    "wdz_ts_poll": (I, [P, P, P]),
+    "wdz_ts_tokens": (I, [P, I, P, I, P]),
     "wdz_reargmax": (I, [P, P, P, I, P, P]),
     "wdz_rules_argmax": (I, [P, P, P, I, I, P, P]),
 }

@@ -92,6 +92,10 @@ struct wdz_engine {
   wdz_rule_desc* g_rules = nullptr;
   struct StepGraph { cudaGraphExec_t exec; long long launches; };
   std::unordered_map<int, StepGraph> step_graphs;
+  std::unordered_map<int, StepGraph> ts_graphs;     // same step with the rule state kept on the device
+  TsState* ts_state = nullptr;                       // [n_slots]
+  int* ts_log = nullptr;                             // [n_slots, max_tokens] generated tokens per slot
+  TsParams ts_params{50257, 50365, 51865, 50, 100, 1u, 2u};
   int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
   int ksplit_override = 0;  // > 0: fixed K split of the residual decode products (tuning experiments)
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
@@ -190,6 +194,8 @@ size_t carve(wdz_engine* e, char* base) {
   e->g_slots = (int*)take(sizeof(int) * (R + 8));
   e->g_next = (int*)take(sizeof(int) * (R + 8));
   e->g_rules = (wdz_rule_desc*)take(sizeof(wdz_rule_desc) * (R + 8));
+  e->ts_state = (TsState*)take(sizeof(TsState) * c.n_slots);
+  e->ts_log = (int*)take(sizeof(int) * (size_t)c.n_slots * c.max_tokens);
   e->part_entries = part_entries_for(c);
   e->part_o = (float*)take(sizeof(float) * e->part_entries * H * HD);
   e->part_ml = (float*)take(sizeof(float) * e->part_entries * H * 2);
@@ -631,9 +637,8 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mpad >> 3) << 17) | ((uint32_t)(tc::BM >> 4) << 24);
   p.cache_k = g.cache_k; p.cache_v = g.cache_v; p.slots = g.slots; p.positions = g.positions;
   p.layer = g.layer; p.n_slots = g.n_slots; p.S = g.S; p.d = g.d;
-  // no L2 prefetch of the next weights here: measured slower at 32-256 rows (it competes with this
-  // kernel's own latency-bound TMA stream); the small-row kernel keeps it
-  p.next_w = nullptr; p.next_bytes = 0;
+  // (no L2 prefetch of the next weights here: measured slower at 32-256 rows, it competes with this
+  // kernel's own latency-bound TMA stream; the small-row kernel keeps it)
   p.status = e->status;
   CUtensorMap mw, mx;
   if (!tc::make_map(&mw, g.W, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * g.N, tc::BM, 2))
@@ -715,6 +720,7 @@ int wdz_engine_destroy(wdz_engine* e) {
   if (e) {
     for (auto& sp : e->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
     for (auto& g : e->step_graphs) cudaGraphExecDestroy(g.second.exec);
+    for (auto& g : e->ts_graphs) cudaGraphExecDestroy(g.second.exec);
     if (e->cap_stream) cudaStreamDestroy(e->cap_stream);
   }
   delete e;
@@ -1181,6 +1187,152 @@ int wdz_decode_step(wdz_engine* e, const int32_t* tokens_dev, const int32_t* slo
       cudaError_t ce = cudaGetLastError();
       return e->fail(WDZ_ECUDA, "logits copy: %s", cudaGetErrorString(ce));
     }
+  }
+  return WDZ_OK;
+}
+
+// ---- decode with the rule state on the device --------------------------------
+__global__ void stage_slots_kernel(const int* __restrict__ slots, int n, int npad, int* __restrict__ g_slots) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < npad) g_slots[r] = r < n ? slots[r] : -1;
+}
+
+static int ts_step_body(wdz_engine* e, int npad, cudaStream_t st) {
+  launch_pdl(e, ts_rules_kernel, dim3((npad + 127) / 128), dim3(128), 0, st, (const int*)e->g_slots, npad,
+             (const TsState*)e->ts_state, e->cfg.n_slots, e->ts_params, e->g_rules, e->g_tokens);
+  WDZ_LAUNCH_CHECK(e, "ts_rules");
+  int rc = decode_step_body(e, e->g_tokens, e->g_slots, e->g_rules, npad, e->g_next, st);
+  if (rc) return rc;
+  launch_pdl(e, ts_update_kernel, dim3((npad + 127) / 128), dim3(128), 0, st, e->g_slots, npad,
+             (const int*)e->g_next, e->ts_state, e->cfg.n_slots, e->ts_params, e->ts_log, e->cfg.max_tokens);
+  WDZ_LAUNCH_CHECK(e, "ts_update");
+  return WDZ_OK;
+}
+
+int wdz_ts_configure(wdz_engine* e, int eot, int ts_begin, int ts_end, int first_timing_max,
+                     int open_after_close_span, uint32_t bit_special, uint32_t bit_timings) {
+  if (!e) return WDZ_EINVAL;
+  if (eot < 0 || ts_begin < 0 || ts_end < ts_begin || ts_end >= e->cfg.n_vocab || eot >= e->cfg.n_vocab)
+    return e->fail(WDZ_EINVAL, "wdz_ts_configure: token ids outside the vocabulary");
+  e->ts_params = TsParams{eot, ts_begin, ts_end, first_timing_max, open_after_close_span, bit_special, bit_timings};
+  for (auto& g : e->ts_graphs) cudaGraphExecDestroy(g.second.exec);   // captured graphs carry the old constants
+  e->ts_graphs.clear();
+  return WDZ_OK;
+}
+
+int wdz_ts_reset(wdz_engine* e, const int32_t* slot_ids_dev, const int32_t* max_new_dev, int n, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!slot_ids_dev || !max_new_dev || n < 0) return e->fail(WDZ_EINVAL, "wdz_ts_reset: null argument");
+  if (n == 0) return WDZ_OK;
+  ts_reset_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)s>>>(slot_ids_dev, max_new_dev, n, e->ts_state,
+                                                                 e->cfg.n_slots);
+  WDZ_LAUNCH_CHECK(e, "ts_reset");
+  return WDZ_OK;
+}
+
+int wdz_ts_first(wdz_engine* e, const float* logits_dev, const int32_t* slot_ids_dev, int n, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!logits_dev || !slot_ids_dev || n < 0) return e->fail(WDZ_EINVAL, "wdz_ts_first: null argument");
+  if (n == 0) return WDZ_OK;
+  if (n > e->cfg.max_rows) return e->fail(WDZ_ECAPACITY, "wdz_ts_first: %d rows > max_rows %d", n, e->cfg.max_rows);
+  cudaStream_t st = (cudaStream_t)s;
+  ts_rules_kernel<<<(n + 127) / 128, 128, 0, st>>>(slot_ids_dev, n, e->ts_state, e->cfg.n_slots, e->ts_params,
+                                                    e->g_rules, e->g_tokens);
+  WDZ_LAUNCH_CHECK(e, "ts_rules");
+  if ((rc = rules_launch(e, logits_dev, nullptr, e->g_rules, n, 1, e->g_next, st))) return rc;
+  // the update kernel edits its row list in place (finished rows are dropped): work on the staged copy
+  stage_slots_kernel<<<(n + 127) / 128, 128, 0, st>>>(slot_ids_dev, n, n, e->g_slots);
+  ts_update_kernel<<<(n + 127) / 128, 128, 0, st>>>(e->g_slots, n, e->g_next, e->ts_state, e->cfg.n_slots,
+                                                     e->ts_params, e->ts_log, e->cfg.max_tokens);
+  WDZ_LAUNCH_CHECK(e, "ts_update");
+  return WDZ_OK;
+}
+
+int wdz_ts_steps(wdz_engine* e, const int32_t* slot_ids_dev, int n, int k, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!slot_ids_dev || n < 0 || k < 0) return e->fail(WDZ_EINVAL, "wdz_ts_steps: bad argument");
+  if (n == 0 || k == 0) return WDZ_OK;
+  const int cap = e->cfg.max_rows < e->max_emit ? e->cfg.max_rows : e->max_emit;
+  if (n > cap) return e->fail(WDZ_ECAPACITY, "wdz_ts_steps: %d rows > capacity %d", n, cap);
+  cudaStream_t st = (cudaStream_t)s;
+  int npad = (n + 7) / 8 * 8;
+  if (npad > cap) npad = n;
+  stage_slots_kernel<<<(npad + 127) / 128, 128, 0, st>>>(slot_ids_dev, n, npad, e->g_slots);
+  WDZ_LAUNCH_CHECK(e, "stage_slots");
+  const bool use_graph = !(e->cfg.flags & WDZ_FLAG_NO_GRAPH) && !e->profiling;
+  if (!use_graph) {
+    for (int i = 0; i < k; ++i)
+      if ((rc = ts_step_body(e, npad, st))) return rc;
+    e->last_emit = npad;
+    return WDZ_OK;
+  }
+  auto it = e->ts_graphs.find(npad);
+  if (it == e->ts_graphs.end()) {
+    const long long before = e->launches;
+    cudaGraph_t graph = nullptr;
+    if (!e->cap_stream && cudaStreamCreateWithFlags(&e->cap_stream, cudaStreamNonBlocking) != cudaSuccess) {
+      cudaError_t ce0 = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "capture stream: %s", cudaGetErrorString(ce0));
+    }
+    if (cudaStreamBeginCapture(e->cap_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      cudaError_t ce0 = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "graph capture begin: %s", cudaGetErrorString(ce0));
+    }
+    rc = ts_step_body(e, npad, e->cap_stream);
+    cudaError_t ce = cudaStreamEndCapture(e->cap_stream, &graph);
+    if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (ce != cudaSuccess || !graph) {
+      cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "graph capture end: %s", cudaGetErrorString(ce));
+    }
+    wdz_engine::StepGraph g{};
+    ce = cudaGraphInstantiate(&g.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) {
+      cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "graph instantiate: %s", cudaGetErrorString(ce));
+    }
+    g.launches = e->launches - before;
+    e->launches = before;
+    it = e->ts_graphs.emplace(npad, g).first;
+  }
+  for (int i = 0; i < k; ++i) {
+    if (cudaGraphLaunch(it->second.exec, st) != cudaSuccess) {
+      cudaError_t ce = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "graph launch: %s", cudaGetErrorString(ce));
+    }
+    e->launches += it->second.launches;
+  }
+  e->last_emit = npad;
+  return WDZ_OK;
+}
+
+int wdz_ts_poll(wdz_engine* e, int32_t* out_host, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!out_host) return e->fail(WDZ_EINVAL, "wdz_ts_poll: null argument");
+  cudaStream_t st = (cudaStream_t)s;
+  if (cudaMemcpyAsync(out_host, e->ts_state, sizeof(TsState) * e->cfg.n_slots, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "rule state read: %s", cudaGetErrorString(ce));
+  }
+  return WDZ_OK;
+}
+
+int wdz_ts_tokens(wdz_engine* e, int slot, int32_t* out_host, int cap, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!out_host || slot < 0 || slot >= e->cfg.n_slots || cap < 0) return e->fail(WDZ_EINVAL, "wdz_ts_tokens: bad argument");
+  if (cap > e->cfg.max_tokens) cap = e->cfg.max_tokens;
+  cudaStream_t st = (cudaStream_t)s;
+  if (cudaMemcpyAsync(out_host, e->ts_log + (size_t)slot * e->cfg.max_tokens, sizeof(int) * cap,
+                      cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaError_t ce = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "token log read: %s", cudaGetErrorString(ce));
   }
   return WDZ_OK;
 }

@@ -333,7 +333,6 @@ struct TcSwapParams {
   uint32_t idesc;
   bf16* cache_k; bf16* cache_v; const int* slots; const int* positions;
   int layer, n_slots, S, d;
-  const void* next_w; size_t next_bytes;   // weights of the next product, prefetched into L2 by the idle lanes
   DevStatus* status;
 };
 
@@ -412,17 +411,6 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
   } else {
     const int quad = warp & 3;
-    if (p.next_w) {
-      // the epilogue warps have nothing to do until the accumulator is complete: they ask L2 for this
-      // CTA's share of the next product's weights, in 128-byte lines
-      const size_t lines = (p.next_bytes + 127) >> 7;
-      const int n_cta = gridDim.x * gridDim.y, cta = blockIdx.y * gridDim.x + blockIdx.x;
-      const size_t per = (lines + n_cta - 1) / n_cta;
-      const size_t lo = per * cta, hi = lo + per < lines ? lo + per : lines;
-      const char* base = reinterpret_cast<const char*>(p.next_w);
-      for (size_t i = lo + (threadIdx.x - 64); i < hi; i += 128)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (i << 7)));
-    }
     bool ok = mbar_wait(acc_full, 0, abort_flag, p.status);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {

@@ -98,3 +98,128 @@ rules_argmax_kernel(const float* __restrict__ logits, int64_t ld, const int* __r
 }
 
 }  // namespace wdz
+
+// ---------------------------------------------------------------------------
+// Token-level rule state on the device.  The timestamp-pair rules need only a
+// few integers per slot (how many tokens, parity and value of the last
+// timestamp, the last ten text tokens), so the per-step host round trip of the
+// reference (classify on the host, upload masks, download ids;
+// decoding.py:1098-1456, 1766) can be dropped for them: one kernel turns each
+// active slot's state into its rule descriptor and input token, and after the
+// argmax another absorbs the new token.  Several decode steps can then be
+// queued back to back; the host only polls the states.
+// ---------------------------------------------------------------------------
+namespace wdz {
+
+struct TsParams {
+  int eot, ts_begin, ts_end;        // 50257, 50365, 51865 for the multilingual vocabulary
+  int first_timing_max;             // first timestamp within this many 0.02 s steps
+  int open_after_close_span;        // next opening timestamp within this many steps of the last closing one
+  uint32_t bit_special, bit_timings;  // class-table bits of the special and of the timestamp tokens
+};
+
+struct TsState {
+  int max_new, n_new, timing_count, last_timing, last_was_timing, n_recent, done, last_token;
+  int recent[10];
+  int pad[6];
+};  // 96 bytes
+
+__global__ void ts_reset_kernel(const int* __restrict__ slots, const int* __restrict__ max_new, int n,
+                                TsState* __restrict__ st, int n_slots) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  const int s = slots[r];
+  if (s < 0 || s >= n_slots) return;
+  TsState z{};
+  z.max_new = max_new[r];
+  z.last_timing = -1;
+  st[s] = z;
+}
+
+// rules[r] and tokens[r] for the row of slot slots[r] (slot < 0: padded row, forced token 0).
+__global__ void ts_rules_kernel(const int* __restrict__ slots, int n, const TsState* __restrict__ st, int n_slots,
+                                TsParams tp, wdz_rule_desc* __restrict__ rules, int* __restrict__ tokens) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  wdz_rule_desc d{};
+  d.forced_id = -1;
+  const int slot = slots[r];
+  if (slot < 0 || slot >= n_slots) {
+    d.forced_id = 0;
+    rules[r] = d;
+    tokens[r] = 0;
+    return;
+  }
+  const TsState s = st[slot];
+  tokens[r] = s.last_token;
+  const int n_timings = tp.ts_end - tp.ts_begin + 1;
+  if (s.done || s.n_new >= s.max_new) {
+    d.forced_id = tp.eot;
+  } else if (s.timing_count == 0) {
+    d.mode = WDZ_MODE_ALL_EXCEPT_RANGE;
+    d.arg0 = tp.ts_begin;
+    d.arg1 = tp.ts_begin + tp.first_timing_max + 1;
+  } else if (s.timing_count & 1) {
+    if (s.last_was_timing) {
+      d.table_bits = tp.bit_special | tp.bit_timings;          // a word must follow an opening timestamp
+    } else {
+      d.table_bits = tp.bit_special;                            // text, or a closing timestamp later than the opening one
+      d.prefix_begin = tp.ts_begin;
+      d.prefix_end = tp.ts_begin + s.last_timing + 1;
+    }
+    d.n_pen = s.n_recent;
+    for (int i = 0; i < 10; ++i) d.pen_ids[i] = s.recent[i];
+  } else if (s.last_timing >= n_timings - 1) {
+    d.forced_id = tp.eot;
+  } else {                                                      // between pairs: next opening timestamp, or EOT
+    d.mode = WDZ_MODE_ALL_EXCEPT_RANGE;
+    d.arg0 = tp.ts_begin + s.last_timing;
+    d.arg1 = min(tp.ts_end + 1, d.arg0 + tp.open_after_close_span);
+    d.n_clear = 1;
+    d.clear_ids[0] = tp.eot;
+  }
+  rules[r] = d;
+}
+
+// Absorbs next[r] into the state of slot slots[r] and appends it to the slot's token log.
+// A row whose slot finishes is dropped from the row list (slot := -1) so that the remaining steps
+// queued by the same call skip it in every kernel.
+__global__ void ts_update_kernel(int* __restrict__ slots, int n, const int* __restrict__ next,
+                                 TsState* __restrict__ st, int n_slots, TsParams tp, int* __restrict__ tok_log,
+                                 int log_stride) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  const int slot = slots[r];
+  if (slot < 0 || slot >= n_slots) return;
+  TsState s = st[slot];
+  if (s.done) { slots[r] = -1; return; }
+  const int tok = next[r];
+  if (s.n_new < log_stride) tok_log[(int64_t)slot * log_stride + s.n_new] = tok;
+  s.n_new += 1;
+  s.last_token = tok;
+  if (tok == tp.eot || tok < 0) {
+    s.done = 1;
+    slots[r] = -1;
+  } else if (tok >= tp.ts_begin && tok <= tp.ts_end) {
+    s.timing_count += 1;
+    s.last_timing = tok - tp.ts_begin;
+    s.last_was_timing = 1;
+  } else {
+    s.last_was_timing = 0;
+    if (s.n_recent >= 10) {
+      for (int i = 0; i < 9; ++i) s.recent[i] = s.recent[i + 1];
+      s.recent[9] = tok;
+    } else {
+      s.recent[s.n_recent++] = tok;
+    }
+  }
+  st[slot] = s;
+}
+
+}  // namespace wdz

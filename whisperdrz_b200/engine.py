@@ -367,6 +367,32 @@ class Engine:
             None if logits is None else logits.data_ptr(), self._stream()))
         return (out, logits) if want_logits else out
 
+    # ------------------------------------------- rule state kept on the device
+    def ts_reset(self, slots, max_new) -> None:
+        s, m = self._i32(slots), self._i32(max_new)
+        self._check(self.lib.wdz_ts_reset(self.h, s.data_ptr(), m.data_ptr(), s.numel(), self._stream()))
+
+    def ts_first(self, logits: torch.Tensor, slots) -> None:
+        logits = logits.to(device=self.device, dtype=torch.float32).contiguous()
+        s = self._i32(slots)
+        self._check(self.lib.wdz_ts_first(self.h, logits.data_ptr(), s.data_ptr(), s.numel(), self._stream()))
+
+    def ts_steps(self, slots, k: int) -> None:
+        s = self._i32(slots)
+        self._check(self.lib.wdz_ts_steps(self.h, s.data_ptr(), s.numel(), int(k), self._stream()))
+
+    def ts_poll(self) -> np.ndarray:
+        """int32 [n_slots, 24]: max_new, n_new, timing_count, last_timing, last_was_timing, n_recent, done,
+        last_token, recent[10], spare[6]."""
+        out = np.empty((self.n_slots, 24), dtype=np.int32)
+        self._check(self.lib.wdz_ts_poll(self.h, out.ctypes.data, self._stream()))
+        return out
+
+    def ts_tokens(self, slot: int, n: int) -> list[int]:
+        out = np.empty(max(n, 1), dtype=np.int32)
+        self._check(self.lib.wdz_ts_tokens(self.h, int(slot), out.ctypes.data, int(n), self._stream()))
+        return out[:n].tolist()
+
     def reargmax(self, rows, rules) -> torch.Tensor:
         r = self._i32(rows)
         rd = self.rules_to_device(rules)

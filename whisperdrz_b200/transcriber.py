@@ -72,14 +72,17 @@ def rules_to_array(rules: list[dict]) -> np.ndarray:
 class Transcriber:
     def __init__(self, engine, BS: int | None = None, max_audio_length: float = 30.0,
                  max_new_tokens: int = 224, lang: str | None = "en", use_rules: bool = True,
-                 text_decoder=None, max_continuations: int = 20):
+                 text_decoder=None, max_continuations: int = 20, device_rules: bool | None = None,
+                 steps_per_poll: int = 8):
         """engine: ``whisperdrz_b200.engine.Engine`` (or an object with the same
         methods).  BS: concurrent slots, at most the engine's.  max_new_tokens:
         generated tokens per 30 s window before EOT is forced.  text_decoder:
         optional ``list[int] -> str`` (the tokenizer is not part of this path).
         max_continuations: a window that ran out of tokens before the end of its
         chunk is continued from its last closing timestamp, at most this many
-        times (transcriber.py:1283-1334; 0 disables)."""
+        times (transcriber.py:1283-1334; 0 disables).  device_rules: keep the
+        token-level rule state on the GPU and queue ``steps_per_poll`` decode
+        steps per host round trip (default: on when the engine offers it)."""
         self.engine = engine
         self.BS = BS or engine.n_slots
         if self.BS > engine.n_slots:
@@ -89,6 +92,9 @@ class Transcriber:
         self.use_rules = use_rules
         self.text_decoder = text_decoder
         self.max_continuations = max_continuations
+        self.device_rules = (hasattr(engine, "ts_steps") and use_rules) if device_rules is None else device_rules
+        self.steps_per_poll = max(1, steps_per_poll)
+        self._tok_cache: dict[int, list] = {}
         self.init_tokens = [TOK_SOT, TOK_LANG_EN, TOK_TRANSCRIBE] if lang else [TOK_SOT]
         if len(self.init_tokens) + max_new_tokens > engine.max_tokens:
             raise ValueError("prompt + max_new_tokens exceed the KV cache length")
@@ -185,8 +191,12 @@ class Transcriber:
             xa = eng.encode(mel)
             ids = [s.index for s in grp]
             logits = eng.prefill(xa, ids, [self.init_tokens] * len(grp))
-            rules = self._rules_dev(self.rule_state.rules_array(ids)) if self.use_rules else None
-            self._accept(grp, eng.rules_argmax(logits, rules).tolist())
+            if self.device_rules:
+                eng.ts_reset(ids, [self.max_new_tokens] * len(ids))
+                eng.ts_first(logits, ids)
+            else:
+                rules = self._rules_dev(self.rule_state.rules_array(ids)) if self.use_rules else None
+                self._accept(grp, eng.rules_argmax(logits, rules).tolist())
 
     def _rules_dev(self, rules) -> torch.Tensor:
         """int32 [n, 32] descriptor array (or a list of rule dicts) -> device tensor."""
@@ -207,7 +217,8 @@ class Transcriber:
     def _finish(self, slot: Slot) -> dict | None:
         """Emits a finished slot, or turns it into a continuation window (returns None)."""
         c = slot.chunk
-        toks = [t for t in self.rule_state.slot_tokens(slot.index) if t != TOK_EOT]
+        raw = self._tok_cache.pop(slot.index) if self.device_rules else self.rule_state.slot_tokens(slot.index)
+        toks = [t for t in raw if t != TOK_EOT]
         base = c.get("offset", 0.0) + slot.win_offset
         segs = token_segments(toks, base)
         duration = c.get("duration", 0.0)
@@ -260,7 +271,23 @@ class Transcriber:
         if new:
             self._prefill_slots(new)
         active = [s for s in self.states if s.status == "started"]
-        if active:
+        if active and self.device_rules:
+            # several steps per host round trip: rules, argmax and state updates all stay on the GPU
+            ids = [s.index for s in active]
+            eng.ts_steps(ids, self.steps_per_poll)
+            self.steps += self.steps_per_poll
+            self.launch_rows += len(active) * self.steps_per_poll
+            st = eng.ts_poll()
+            for s in active:
+                row = st[s.index]
+                if row[6]:                                   # done
+                    n_new, max_new = int(row[1]), int(row[0])
+                    toks = eng.ts_tokens(s.index, n_new)
+                    self._tok_cache[s.index] = toks
+                    s.status = "finished"
+                    last = toks[-1] if toks else TOK_EOT
+                    s.stop_reason = "max_tokens" if n_new > max_new else ("eot" if last == TOK_EOT else "nan_logits")
+        elif active:
             ids = [s.index for s in active]
             rules = self._rules_dev(self.rule_state.rules_array(ids)) if self.use_rules else None
             nxt = eng.decode_step([s.last_token for s in active], ids, rules=rules)
