@@ -131,6 +131,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same load without the wait, and the wait with the registers threaded through it, so that a
+// second load can be in flight while the first one's values are used.
+__device__ __forceinline__ void tmem_ld32_raw(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) asm volatile("" : "+r"(r[i]));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
@@ -420,31 +439,59 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       float bias = 0.0f;
       if (n_ok && p.bias && blockIdx.y == 0) bias = to_f(p.bias[n]);
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < p.mpad; c += 32) {
-        float v[32];
-        tmem_ld32(taddr + c, v);
-        if (!n_ok) continue;
+      // 32 rows per TMEM load; the load of the next 32 rows is in flight while these are written out
+      auto emit = [&](int c, const uint32_t (&r)[32]) {
+        if (!n_ok) return;
+        const int rows = min(32, p.M - c);
+        if (p.epi == EPI_RESID) {
+          float* dst = reinterpret_cast<float*>(p.y) + (int64_t)c * p.ldy + n;
+          if (gridDim.y > 1) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int m = c + j;
-          if (m >= p.M) break;
-          const float val = v[j] + bias;
-          if (p.epi == EPI_RESID) {
-            float* dst = reinterpret_cast<float*>(p.y) + (int64_t)m * p.ldy + n;
-            if (gridDim.y > 1) atomicAdd(dst, val); else *dst += val;
-          } else if (p.epi == EPI_GELU) {
-            reinterpret_cast<bf16*>(p.y)[(int64_t)m * p.ldy + n] = from_f<bf16>(gelu_erf(val));
-          } else if (p.epi == EPI_SW_QKV_CACHE && n >= p.d) {
-            const int s = p.slots[m], pos = p.positions[m];
-            if (s >= 0 && s < p.n_slots && pos >= 0 && pos < p.S) {
-              const bool is_v = n >= 2 * p.d;
-              bf16* dst = is_v ? p.cache_v : p.cache_k;
-              dst[(((int64_t)p.layer * p.n_slots + s) * p.S + pos) * p.d + (n - (is_v ? 2 : 1) * p.d)] = from_f<bf16>(val);
-            }
+            for (int j = 0; j < 32; ++j)
+              if (j < rows) atomicAdd(dst + (int64_t)j * p.ldy, __uint_as_float(r[j]) + bias);
           } else {
-            reinterpret_cast<float*>(p.y)[(int64_t)m * p.ldy + n] = val;
+            float old[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) old[j] = j < rows ? dst[(int64_t)j * p.ldy] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < rows) dst[(int64_t)j * p.ldy] = old[j] + __uint_as_float(r[j]) + bias;
           }
+        } else if (p.epi == EPI_GELU) {
+          bf16* dst = reinterpret_cast<bf16*>(p.y) + (int64_t)c * p.ldy + n;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < rows) dst[(int64_t)j * p.ldy] = from_f<bf16>(gelu_erf(__uint_as_float(r[j]) + bias));
+        } else if (p.epi == EPI_SW_QKV_CACHE && n >= p.d) {
+          const bool is_v = n >= 2 * p.d;
+          bf16* cache = is_v ? p.cache_v : p.cache_k;
+          const int col = n - (is_v ? 2 : 1) * p.d;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j < rows) {
+              const int sl = p.slots[c + j], pos = p.positions[c + j];
+              if (sl >= 0 && sl < p.n_slots && pos >= 0 && pos < p.S)
+                cache[(((int64_t)p.layer * p.n_slots + sl) * p.S + pos) * p.d + col] =
+                    from_f<bf16>(__uint_as_float(r[j]) + bias);
+            }
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(p.y) + (int64_t)c * p.ldy + n;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < rows) dst[(int64_t)j * p.ldy] = __uint_as_float(r[j]) + bias;
+        }
+      };
+      uint32_t ra[32], rb[32];
+      tmem_ld32_raw(taddr, ra);
+      for (int c = 0; c < p.mpad; c += 64) {
+        tmem_wait_ld(ra);
+        if (c + 32 < p.mpad) tmem_ld32_raw(taddr + c + 32, rb);
+        if (c < p.M) emit(c, ra);
+        if (c + 32 < p.mpad) {
+          tmem_wait_ld(rb);
+          if (c + 64 < p.mpad) tmem_ld32_raw(taddr + c + 64, ra);
+          if (c + 32 < p.M) emit(c + 32, rb);
         }
       }
       tc_fence_before();
