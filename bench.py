@@ -234,8 +234,8 @@ def main():
     eng.profile(False)
     peak, peak_kind = peaks()
     ca = prof["cross_attn"]
-    # dram read+write per row per launch of this kernel from the ncu capture summarised in
-    # profiles/attn_dec_stream_kernel_decode_32rows.md (32 rows: 245.944 MB + 4.606 MB); grows linearly with rows
+    # dram read+write per row per launch of this kernel from an ncu capture of a 32-row launch
+    # (245.944 MB read + 4.606 MB written); every row has its own K/V, so traffic grows linearly with rows
     traffic_per_row = (245.944064e6 + 4.605952e6) / 32
     per_launch_ms = ca["ms"] / max(ca["launches"], 1)
     per_launch_bytes = ca["work"] / max(ca["launches"], 1)

@@ -1,5 +1,5 @@
-"""Timings of the other BASELINE.json workloads on one GPU (bench.py times the
-batched end-to-end case):
+"""Timings of the named workloads other than the batched end-to-end case that
+bench.py times, on one GPU:
 
     python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5]
 
