@@ -442,3 +442,48 @@ def test_decode_shaped_linear_matches_fp32_reference(small_bf16, M):
     e.linear_rows(x, w, b, out=acc)
     assert (acc.cpu() - (ref + 0.5)).abs().max() / ref.abs().max() < 2e-5
     e.device_status()
+
+
+def test_device_rule_state_through_the_abi(small_f32):
+    """wdz_ts_*: reset, first token, k queued steps, poll and token log against
+    the host rule state driving wdz_decode_step one step at a time."""
+    from whisperdrz_b200 import rules as R
+    from whisperdrz_b200.transcriber import rules_to_array
+    e, dims, sd = small_f32
+    # the fixture engine has no class tables: build one that has them
+    from whisperdrz_b200.engine import Engine
+    eng = Engine(dims, sd, dtype=torch.float32, n_slots=4, max_clips=2, tables=R.timestamp_tables(dims.n_vocab))
+    audio = synth.clips([51, 52])
+    xa = eng.encode(eng.logmel(torch.from_numpy(audio).cuda()))
+    prompt = [[50258, 50259, 50360]] * 2
+    budgets = [9, 30]
+    # host rules, one step per call
+    slots = [1, 3]
+    logits = eng.prefill(xa, slots, prompt)
+    rows = [R.RowState(max_new=b) for b in budgets]
+    cur = eng.rules_argmax(logits, torch.from_numpy(rules_to_array([r.rule() for r in rows])).cuda()).tolist()
+    for r, t in zip(rows, cur):
+        r.update(t)
+    while not all(r.done for r in rows):
+        act = [i for i, r in enumerate(rows) if not r.done]
+        nxt = eng.decode_step([rows[i].tokens[-1] for i in act], [slots[i] for i in act],
+                              rules=torch.from_numpy(rules_to_array([rows[i].rule() for i in act])).cuda()).tolist()
+        for i, t in zip(act, nxt):
+            rows[i].update(t)
+    # device rules: everything queued, finished rows drop out on the device
+    logits = eng.prefill(xa, slots, prompt)
+    eng.ts_reset(slots, budgets)
+    eng.ts_first(logits, slots)
+    eng.ts_steps(slots, 7)
+    st = eng.ts_poll()
+    assert st[1, 0] == 9 and st[1, 1] == 8 and st[1, 6] == 0          # 1 + 7 tokens, not done yet
+    eng.ts_steps(slots, 40)                                            # more than either slot needs
+    st = eng.ts_poll()
+    for i, s in enumerate(slots):
+        assert st[s, 6] == 1 and st[s, 1] == len(rows[i].tokens)
+        assert eng.ts_tokens(s, int(st[s, 1])) == rows[i].tokens
+    # a finished slot stops growing its KV: length = prompt + generated tokens that were fed back
+    lens = eng.seq_lens()
+    assert [lens[s] for s in slots] == [3 + len(r.tokens) - 1 for r in rows]
+    eng.device_status()
+    eng.close()

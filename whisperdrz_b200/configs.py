@@ -61,6 +61,17 @@ def cfg1(dims, sd):
             return torch.cat(toks).tolist()
         ms, toks = _timed(run, reps=2)
         res[name] = {"latency_ms": ms, "rtfx": 30000.0 / ms, "tokens": len(toks)}
+        if dt == torch.bfloat16:
+            # the same decode with the rule state on the device: all 223 steps queued by one call
+            def run_dev():
+                xa = e.encode(e.logmel(audio))
+                logits = e.prefill(xa, [0], [[50258, 50259, 50360, 50365]])
+                e.ts_reset([0], [224])
+                e.ts_first(logits, [0])
+                e.ts_steps([0], 223)
+                return e.ts_tokens(0, int(e.ts_poll()[0, 1]))
+            ms2, toks2 = _timed(run_dev, reps=2)
+            res["bf16_device_rules"] = {"latency_ms": ms2, "rtfx": 30000.0 / ms2, "tokens": len(toks2)}
         e.close()
     return res
 
