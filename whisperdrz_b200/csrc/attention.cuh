@@ -432,12 +432,22 @@ __global__ void attn_dec_combine_kernel(AttnDecParams p) {
     L = L * resc + warp_sum(ls * w);
     o0 *= resc; o1 *= resc;
     const int cnt = min(32, nsplit - s0);
-#pragma unroll 4
-    for (int i = 0; i < cnt; ++i) {
-      const float wi = __shfl_sync(0xffffffffu, w, i);
-      const float* po = p.part_o + (base + (int64_t)(s0 + i) * H) * HD;
-      o0 = fmaf(po[lane], wi, o0);
-      o1 = fmaf(po[32 + lane], wi, o1);
+    // sixteen splits at a time: all their loads are issued before the first one is used
+    for (int i0 = 0; i0 < cnt; i0 += 16) {
+      float x0[16], x1[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const bool ok = i0 + u < cnt;
+        const float* po = p.part_o + (base + (int64_t)(s0 + (ok ? i0 + u : 0)) * H) * HD;
+        x0[u] = ok ? po[lane] : 0.0f;
+        x1[u] = ok ? po[32 + lane] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const float wi = __shfl_sync(0xffffffffu, w, (i0 + u) & 31);
+        o0 = fmaf(x0[u], wi, o0);
+        o1 = fmaf(x1[u], wi, o1);
+      }
     }
     M = M_new;
   }

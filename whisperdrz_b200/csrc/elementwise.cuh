@@ -7,10 +7,32 @@
 
 namespace wdz {
 
-// y[r] = LN(x[src(r)]) * gamma + beta.  One warp per row; the row is read
-// once with 16-byte loads that are all issued before the first use (rows of
-// up to 2048 elements live in registers), then mean, centred variance and the
-// affine output are computed from the registers.  d % 4 == 0, d <= 2048.
+// Four consecutive parameters / outputs at once (16 bytes of fp32 or 8 bytes of bf16).
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+  const uint2 t = __ldg(reinterpret_cast<const uint2*>(p));
+  v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+  v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<uint32_t*>(&a);
+  t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+// y[r] = LN(x[src(r)]) * gamma + beta over the fp32 residual stream, d % 4 == 0, d <= 2048.
+// Two shapes of the same arithmetic (mean, then centred variance, both from registers; the row is
+// read once): one warp per row for the tens of thousands of encoder rows, and one 128-thread CTA per
+// row for the few decode rows, where the time is a chain of memory latencies, not bandwidth - there
+// every thread issues its (at most four) loads of x, gamma and beta at once.
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(128)
 layernorm_kernel(const float* __restrict__ x, int64_t ldx, const int* __restrict__ row_idx,
@@ -48,11 +70,73 @@ layernorm_kernel(const float* __restrict__ x, int64_t ldx, const int* __restrict
   for (int i = 0; i < MAXV; ++i) {
     const int j = lane + 32 * i;
     if (j < nv) {
-      const int c = 4 * j;
-      yr[c] = from_f<TO>((v[i].x - mean) * rstd * to_f(gamma[c]) + to_f(beta[c]));
-      yr[c + 1] = from_f<TO>((v[i].y - mean) * rstd * to_f(gamma[c + 1]) + to_f(beta[c + 1]));
-      yr[c + 2] = from_f<TO>((v[i].z - mean) * rstd * to_f(gamma[c + 2]) + to_f(beta[c + 2]));
-      yr[c + 3] = from_f<TO>((v[i].w - mean) * rstd * to_f(gamma[c + 3]) + to_f(beta[c + 3]));
+      float g[4], bt[4], o[4];
+      load4(gamma + 4 * j, g);
+      load4(beta + 4 * j, bt);
+      o[0] = (v[i].x - mean) * rstd * g[0] + bt[0];
+      o[1] = (v[i].y - mean) * rstd * g[1] + bt[1];
+      o[2] = (v[i].z - mean) * rstd * g[2] + bt[2];
+      o[3] = (v[i].w - mean) * rstd * g[3] + bt[3];
+      store4(yr + 4 * j, o);
+    }
+  }
+}
+
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(128)
+layernorm_row_kernel(const float* __restrict__ x, int64_t ldx, const int* __restrict__ row_idx,
+                     const TP* __restrict__ gamma, const TP* __restrict__ beta,
+                     TO* __restrict__ y, int64_t ldy, int rows, int d) {
+  pdl_trigger();
+  constexpr int MAXI = 4;  // float4 per thread: d <= 2048
+  __shared__ float red[2][4];
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nv = d >> 2;
+  // gamma and beta do not depend on the previous kernel: fetch them before waiting for it
+  float g[MAXI][4], bt[MAXI][4];
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int j = tid + 128 * i;
+    if (j < nv) { load4(gamma + 4 * j, g[i]); load4(beta + 4 * j, bt[i]); }
+  }
+  pdl_wait();
+  const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)(row_idx ? row_idx[r] : r) * ldx);
+  float4 v[MAXI];
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int j = tid + 128 * i;
+    v[i] = j < nv ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  s = warp_sum(s);
+  if (lane == 0) red[0][warp] = s;
+  __syncthreads();
+  const float mean = ((red[0][0] + red[0][1]) + (red[0][2] + red[0][3])) / d;
+  float q = 0.0f;
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    if (tid + 128 * i < nv) {
+      const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, e = v[i].w - mean;
+      q += a * a + b * b + c * c + e * e;
+    }
+  }
+  q = warp_sum(q);
+  if (lane == 0) red[1][warp] = q;
+  __syncthreads();
+  const float rstd = rsqrtf(((red[1][0] + red[1][1]) + (red[1][2] + red[1][3])) / d + 1e-5f);
+  TO* yr = y + (int64_t)r * ldy;
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int j = tid + 128 * i;
+    if (j < nv) {
+      float o[4];
+      o[0] = (v[i].x - mean) * rstd * g[i][0] + bt[i][0];
+      o[1] = (v[i].y - mean) * rstd * g[i][1] + bt[i][1];
+      o[2] = (v[i].z - mean) * rstd * g[i][2] + bt[i][2];
+      o[3] = (v[i].w - mean) * rstd * g[i][3] + bt[i][3];
+      store4(yr + 4 * j, o);
     }
   }
 }

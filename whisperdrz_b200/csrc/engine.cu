@@ -286,6 +286,10 @@ template <typename TP, typename TO>
 int launch_ln(wdz_engine* e, const float* x, int64_t ldx, const int* row_idx, const void* g, const void* b,
               TO* y, int64_t ldy, int rows, int d, cudaStream_t s) {
   if (rows <= 0) return WDZ_OK;
+  if (rows <= 1024)   // few rows: a CTA per row (latency-bound); many rows: a warp per row (bandwidth-bound)
+    launch_pdl(e, layernorm_row_kernel<TP, TO>, dim3(rows), dim3(128), 0, s, x, ldx, row_idx, (const TP*)g,
+               (const TP*)b, y, ldy, rows, d);
+  else
   launch_pdl(e, layernorm_kernel<TP, TO>, dim3((rows + 3) / 4), dim3(128), 0, s, x, ldx, row_idx, (const TP*)g, (const TP*)b, y, ldy, rows, d);
   WDZ_LAUNCH_CHECK(e, "layernorm");
   return WDZ_OK;
