@@ -167,6 +167,12 @@ class Transcriber:
                 buf = torch.zeros(len(grp), 480000, dtype=torch.float32, device=dev)
                 for i, s in enumerate(grp):
                     buf[i, : n[i]] = s.chunk["audio"][: n[i]]
+            elif dev.type == "cuda" and all(isinstance(s.chunk["audio"], torch.Tensor) and s.chunk["audio"].is_pinned()
+                                            and s.chunk["audio"].dtype == torch.float32 for s in grp):
+                # caller-pinned host audio goes to the device directly, one asynchronous copy per chunk
+                buf = torch.zeros(len(grp), 480000, dtype=torch.float32, device=dev)
+                for i, s in enumerate(grp):
+                    buf[i, : n[i]].copy_(s.chunk["audio"][: n[i]], non_blocking=True)
             else:
                 self._pin_audio = getattr(eng, "_pin_audio", None)
                 if self._pin_audio is None:      # one pinned staging buffer per engine, reused for every group
