@@ -487,3 +487,30 @@ def test_device_rule_state_through_the_abi(small_f32):
     assert [lens[s] for s in slots] == [3 + len(r.tokens) - 1 for r in rows]
     eng.device_status()
     eng.close()
+
+
+def test_decode_to_the_last_cache_position(small_f32):
+    """One slot decoded until the self-attention cache is full (448 positions:
+    every split of the ragged attention, the last cache row, the position
+    table's last row), against the oracle; then the engine must refuse nothing
+    and keep the slot length at the cache size."""
+    e, dims, sd = small_f32
+    audio = synth.clips([61])
+    mel = _oracle_mel(audio)
+    xa_ref = oracle.encoder(sd, mel, dims.n_audio_layer, dims.n_audio_head)
+    dec = oracle.SlotDecoder(sd, dims.n_text_layer, dims.n_text_head, 6, dims.n_text_ctx)
+    ref = dec.prefill(torch.tensor([[50258, 50259, 50360]]), xa_ref, [5])[:, -1]
+    got = e.prefill(xa_ref.cuda(), [5], [[50258, 50259, 50360]])
+    rms = ref.pow(2).mean().sqrt()
+    cur = ref.argmax(-1)
+    worst = float((got.cpu() - ref).abs().max() / rms)
+    for step in range(3, dims.n_text_ctx):
+        ref = dec.forward(cur.view(1, 1), [5])[:, 0]
+        nxt, lg = e.decode_step(cur, [5], want_logits=True)
+        if step % 37 == 0 or step >= dims.n_text_ctx - 2:
+            worst = max(worst, float((lg.cpu() - ref).abs().max() / rms))
+            assert int(nxt[0]) == int(ref.argmax(-1))
+        cur = ref.argmax(-1)
+    assert worst < F32_LOGIT_TOL, worst
+    assert e.seq_lens()[5] == dims.n_text_ctx
+    e.device_status()
