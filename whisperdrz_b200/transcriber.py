@@ -73,7 +73,7 @@ class Transcriber:
     def __init__(self, engine, BS: int | None = None, max_audio_length: float = 30.0,
                  max_new_tokens: int = 224, lang: str | None = "en", use_rules: bool = True,
                  text_decoder=None, max_continuations: int = 20, device_rules: bool | None = None,
-                 steps_per_poll: int = 8):
+                 steps_per_poll: int = 8, min_refill: int = 1, max_refill_wait: int = 4):
         """engine: ``whisperdrz_b200.engine.Engine`` (or an object with the same
         methods).  BS: concurrent slots, at most the engine's.  max_new_tokens:
         generated tokens per 30 s window before EOT is forced.  text_decoder:
@@ -82,7 +82,12 @@ class Transcriber:
         chunk is continued from its last closing timestamp, at most this many
         times (transcriber.py:1283-1334; 0 disables).  device_rules: keep the
         token-level rule state on the GPU and queue ``steps_per_poll`` decode
-        steps per host round trip (default: on when the engine offers it)."""
+        steps per host round trip (default: on when the engine offers it).
+        min_refill: while other slots are decoding, new chunks are admitted only
+        when at least this many can be prefilled together (the encoder is far
+        more efficient on a batch of windows), or after ``max_refill_wait``
+        scheduler iterations; the reference refills one by one
+        (transcriber.py:1790-1815, ``min_refill_batch = 1``), which is the default."""
         self.engine = engine
         self.BS = BS or engine.n_slots
         if self.BS > engine.n_slots:
@@ -94,6 +99,8 @@ class Transcriber:
         self.max_continuations = max_continuations
         self.device_rules = (hasattr(engine, "ts_steps") and use_rules) if device_rules is None else device_rules
         self.steps_per_poll = max(1, steps_per_poll)
+        self.min_refill, self.max_refill_wait = max(1, min_refill), max_refill_wait
+        self._refill_waited = 0
         self._tok_cache: dict[int, list] = {}
         self.init_tokens = [TOK_SOT, TOK_LANG_EN, TOK_TRANSCRIBE] if lang else [TOK_SOT]
         if len(self.init_tokens) + max_new_tokens > engine.max_tokens:
@@ -267,13 +274,21 @@ class Transcriber:
         eng = self.engine
         done: list[dict] = []
         new = []
-        for s in self.states:
-            if s.status == "continue":
-                s.status = "started"
-                new.append(s)
-            elif s.status == "ready" and self.pending_chunks:
-                self._init_slot(s, self.pending_chunks.pop(0))
-                new.append(s)
+        cont = [s for s in self.states if s.status == "continue"]
+        free = [s for s in self.states if s.status == "ready"]
+        busy = any(s.status == "started" for s in self.states)
+        n_admit = min(len(free), len(self.pending_chunks))
+        if n_admit and busy and len(cont) + n_admit < self.min_refill and self._refill_waited < self.max_refill_wait:
+            self._refill_waited += 1          # let a larger prefill batch build up while the others decode
+            n_admit, cont = 0, []
+        else:
+            self._refill_waited = 0
+        for s in cont:
+            s.status = "started"
+            new.append(s)
+        for s in free[:n_admit]:
+            self._init_slot(s, self.pending_chunks.pop(0))
+            new.append(s)
         if new:
             self._prefill_slots(new)
         active = [s for s in self.states if s.status == "started"]
