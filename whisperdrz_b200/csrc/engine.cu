@@ -97,6 +97,7 @@ struct wdz_engine {
   int* ts_log = nullptr;                             // [n_slots, max_tokens] generated tokens per slot
   TsParams ts_params{50257, 50365, 51865, 50, 100, 1u, 2u};
   int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
+  int row_tile_override = 0;  // > 0: row tile of the decode products (32..256; tuning experiments)
   int ksplit_override = 0;  // > 0: fixed K split of the residual decode products (tuning experiments)
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
 
@@ -623,14 +624,30 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   if ((((uintptr_t)g.x | (uintptr_t)g.W) & 15) || (g.ldx * 2) % 16) return 1;
   tc::TcSwapParams p{};
   p.bias = g.bias; p.y = g.y; p.ldy = g.ldy; p.M = g.M; p.N = g.N; p.K = g.K;
-  p.mpad = (g.M + 31) / 32 * 32;
+  // Row tile and K split.  A CTA takes in one 64-wide k-block of operands in 0.4 us (32 rows) to 0.8 us (256
+  // rows) and all CTAs together about 6 TB/s, so the work is cut to cover the SMs in ONE wave:
+  //  - complete sums (no K split): the smallest row tile whose CTAs still fit one wave;
+  //  - residual sums (K split, red.global.add): a single row tile when K is long (operand bytes dominate),
+  //    else 64- or 128-row tiles, and as many K splits as fill the wave.
+  const int mpad_all = (g.M + 31) / 32 * 32;
+  const int tiles = (g.N + tc::BM - 1) / tc::BM;
+  p.kblocks = g.K / tc::BK;
+  int row_tile = mpad_all;
+  if (e->row_tile_override > 0) {
+    row_tile = std::min(mpad_all, e->row_tile_override);
+  } else if (epi == EPI_RESID) {
+    if (p.kblocks < 64) row_tile = std::min(mpad_all, g.M <= 128 ? 64 : 128);
+  } else {
+    for (int rt = 32; rt < mpad_all; rt *= 2)
+      if (tiles * ((g.M + rt - 1) / rt) <= e->sm_count) { row_tile = rt; break; }
+  }
+  p.mpad = row_tile;
+  const int row_tiles = (g.M + row_tile - 1) / row_tile;
   p.tmem_cols = 32;
   while (p.tmem_cols < p.mpad) p.tmem_cols <<= 1;
-  p.kblocks = g.K / tc::BK;
-  const int tiles = (g.N + tc::BM - 1) / tc::BM;
   int ksplit = 1;
   if (epi == EPI_RESID) {
-    ksplit = (e->sm_count + tiles - 1) / tiles;
+    ksplit = e->sm_count / (tiles * row_tiles);
     if (e->ksplit_override > 0) ksplit = e->ksplit_override;
     if (ksplit > p.kblocks) ksplit = p.kblocks;
     if (ksplit < 1) ksplit = 1;
@@ -650,7 +667,8 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   if (!tc::make_map(&mx, g.x, (uint64_t)g.K, (uint64_t)g.M, 1, (uint64_t)g.ldx * 2, (uint64_t)g.ldx * 2 * g.M,
                     (uint32_t)p.mpad, 2))
     return 1;
-  launch_pdl(e, tc::gemm_tc_swap_kernel, dim3(tiles, ksplit), dim3(tc::THREADS), tc::SW_SMEM_BYTES, s, mw, mx, p);
+  launch_pdl(e, tc::gemm_tc_swap_kernel, dim3(tiles, ksplit, row_tiles), dim3(tc::THREADS),
+             (size_t)tc::sw_smem_bytes(row_tile), s, mw, mx, p);
   WDZ_LAUNCH_CHECK(e, "gemm_tc_swap");
   return WDZ_OK;
 }
@@ -706,6 +724,7 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
   e->cfg = c;
   e->esz = c.dtype == WDZ_BF16 ? 2 : 4;
   if (const char* ks = getenv("WDZ_KSPLIT")) e->ksplit_override = atoi(ks);
+  if (const char* rt = getenv("WDZ_ROWTILE")) e->row_tile_override = atoi(rt) / 32 * 32;
   if (const char* gm = getenv("WDZ_GEMV_MAX_ROWS")) e->gemv_max_rows = atoi(gm);
   e->enc.resize(c.n_audio_layer);
   e->dec.resize(c.n_text_layer);

@@ -328,24 +328,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 // ---------------------------------------------------------------------------
 // Decode-shaped product on tcgen05 with the operands swapped:
-//   D[feature, row] = W[128-feature tile, K] . x[rows, K]^T
-// so that the 128-wide MMA M dimension is filled by output features and the
-// few dozen to 256 token rows form the MMA N dimension.  W is read from HBM
-// exactly once per call; the x tile (rows x 64 k, at most 32 KB) is re-staged
-// by TMA once per 128 features instead of once per 16.  grid = (feature
-// tiles, K splits); with more than one K split the partial sums are added to
-// the fp32 output with red.global.add (residual-stream epilogue only).
+//   D[feature, row] = W[128-feature tile, K] . x[row tile, K]^T
+// so that the 128-wide MMA M dimension is filled by output features and a
+// tile of 32 to 256 token rows forms the MMA N dimension.  W comes from HBM
+// once per call (row tiles of the same features run together and share it
+// through L2).  grid = (feature tiles, K splits, row tiles): the host picks
+// the row tile and the K split so that the CTAs cover the SMs - a call is
+// bounded by the rate at which one SM takes operand bytes into shared memory
+// (about 0.3-0.4 us per 64-wide k-block), not by the weight stream.  With
+// more than one K split the partial sums are added to the fp32 output with
+// red.global.add (residual-stream epilogue only).
 // Epilogue thread = one feature (TMEM lane), columns = rows.
 // ---------------------------------------------------------------------------
 constexpr int SW_STAGES = 4;
 constexpr int SW_STAGE_BYTES = A_BYTES + 256 * BK * 2;   // W tile + up to 256 rows of x
-constexpr int SW_SMEM_BYTES = SW_STAGES * SW_STAGE_BYTES + 256 + 1024;
+constexpr int SW_SMEM_BYTES = SW_STAGES * SW_STAGE_BYTES + 256 + 1024;   // largest launch
+inline int sw_smem_bytes(int row_tile) { return SW_STAGES * (A_BYTES + row_tile * BK * 2) + 256 + 1024; }
 constexpr int EPI_SW_QKV_CACHE = 16;
 
 struct TcSwapParams {
   const bf16* bias; void* y; int64_t ldy;
   int M, N, K;               // rows, features, contraction
-  int mpad;                  // rows padded to a multiple of 32 (MMA N)
+  int mpad;                  // rows of one CTA's row tile, a multiple of 32 (MMA N)
   int tmem_cols;             // power of two >= mpad, >= 32
   int kb_per_split, kblocks;
   int epi;                   // EPI_STORE (f32) | EPI_GELU (bf16 out) | EPI_RESID (f32 +=) | EPI_SW_QKV_CACHE
@@ -367,7 +371,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const TcSwapParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SW_STAGES * SW_STAGE_BYTES);
+  const uint32_t stage_bytes = A_BYTES + (uint32_t)p.mpad * BK * 2;   // a multiple of 1024
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SW_STAGES * stage_bytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + SW_STAGES;
   uint64_t* acc_full = bars + 2 * SW_STAGES;
@@ -376,6 +381,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x;
+  const int row0 = blockIdx.z * p.mpad;           // first token row of this CTA's row tile
   const int kb0 = blockIdx.y * p.kb_per_split;
   const int kb1 = min(p.kblocks, kb0 + p.kb_per_split);
   const int nkb = kb1 - kb0;   // >= 1 by construction of the grid
@@ -397,7 +403,6 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   pdl_trigger();
   pdl_wait();   // barriers, TMEM and tensor-map prefetch above overlap the previous kernel
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t stage_tx = A_BYTES + (uint32_t)p.mpad * BK * 2;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -405,10 +410,10 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         const int stage = i % SW_STAGES;
         const uint32_t phase = (i / SW_STAGES) & 1;
         if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.status)) break;
-        uint8_t* w_dst = smem + stage * SW_STAGE_BYTES;
-        mbar_expect_tx(full + stage, stage_tx);
+        uint8_t* w_dst = smem + stage * stage_bytes;
+        mbar_expect_tx(full + stage, stage_bytes);
         tma_load_2d(w_dst, &tmW, full + stage, (kb0 + i) * BK, tile * BM);
-        tma_load_2d(w_dst + A_BYTES, &tmX, full + stage, (kb0 + i) * BK, 0);
+        tma_load_2d(w_dst + A_BYTES, &tmX, full + stage, (kb0 + i) * BK, row0);
       }
     }
   } else if (warp == 1) {
@@ -419,7 +424,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         const uint32_t phase = (i / SW_STAGES) & 1;
         if (!(ok = mbar_wait(full + stage, phase, abort_flag, p.status))) break;
         tc_fence_after();
-        const uint32_t w_addr = smem_u32(smem + stage * SW_STAGE_BYTES);
+        const uint32_t w_addr = smem_u32(smem + stage * stage_bytes);
         const uint32_t x_addr = w_addr + A_BYTES;
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k)
@@ -440,7 +445,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       if (n_ok && p.bias && blockIdx.y == 0) bias = to_f(p.bias[n]);
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
       // 32 rows per TMEM load; the load of the next 32 rows is in flight while these are written out
-      auto emit = [&](int c, const uint32_t (&r)[32]) {
+      auto emit = [&](int c, const uint32_t (&r)[32]) {   // c: first token row of the 32 in r
         if (!n_ok) return;
         const int rows = min(32, p.M - c);
         if (p.epi == EPI_RESID) {
@@ -487,11 +492,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       for (int c = 0; c < p.mpad; c += 64) {
         tmem_wait_ld(ra);
         if (c + 32 < p.mpad) tmem_ld32_raw(taddr + c + 32, rb);
-        if (c < p.M) emit(c, ra);
+        if (row0 + c < p.M) emit(row0 + c, ra);
         if (c + 32 < p.mpad) {
           tmem_wait_ld(rb);
           if (c + 64 < p.mpad) tmem_ld32_raw(taddr + c + 64, ra);
-          if (c + 32 < p.M) emit(c + 32, rb);
+          if (row0 + c + 32 < p.M) emit(row0 + c + 32, rb);
         }
       }
       tc_fence_before();
