@@ -424,14 +424,16 @@ def test_transcribe_end_to_end_identical_to_oracle_scheduler():
     e.close()
 
 
-@pytest.mark.parametrize("M", [1, 8, 16, 40, 256, 300])
-def test_decode_shaped_linear_matches_fp32_reference(small_bf16, M):
+@pytest.mark.parametrize("M,N", [(1, 1280), (8, 1280), (16, 1280), (40, 1280), (256, 1280), (300, 1280),
+                                 (100, 1280), (200, 1280), (200, 3840), (129, 5120), (72, 2000)])
+def test_decode_shaped_linear_matches_fp32_reference(small_bf16, M, N):
     """wdz_linear_rows: the mma.sync weight-streaming kernel (<= 16 rows) and the
-    operand-swapped tcgen05 kernel (more rows, chunked above 256) against an fp32
+    operand-swapped tcgen05 kernel (more rows: ragged row tiles, K splits, feature
+    counts that are no multiple of 128, chunks above 256 rows) against an fp32
     product of the same bf16 operands, storing and accumulating."""
     e, _, _ = small_bf16
     g = torch.Generator().manual_seed(M)
-    N, K = 1280, 1024
+    K = 1024
     x = torch.randn(M, K, generator=g).bfloat16()
     w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16()
     b = (torch.randn(N, generator=g) * 0.1).bfloat16()
