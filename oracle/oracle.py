@@ -287,3 +287,112 @@ def rules_argmax(logits: torch.Tensor, rules: list[dict], tables: torch.Tensor,
             val = torch.where(pm, penalized, val)
         out[b] = int(torch.argmax(val))
     return out
+
+
+# --------------------------------------------------------------------------- #
+# word-timing alignment (src/whisperdrz/dtw_align.py: device steps of
+# fill_word_timings_batch, 1112-1240)
+# --------------------------------------------------------------------------- #
+def align_scores(sd: dict, tokens: torch.Tensor, xa: torch.Tensor, n_layer: int, n_head: int,
+                 heads: list[tuple[int, int]]) -> torch.Tensor:
+    """Teacher-forced uncached decoder pass (``TextDecoder.forward`` model.py:547-568 without the optional
+    timing embedding, blocks as model.py:396-401) capturing, per decoder block, the cross-attention query
+    and key projections (``CrossAttnCapture`` dtw_align.py:498-551), then ``compute_attention``
+    (dtw_align.py:553-586): QK^T of the selected (layer, head) pairs with the hd^-0.25 scale on each side,
+    no softmax.  tokens int64 [B, T], xa [B, Ta, d] -> f32 [B, n_sel, T, Ta].  Layers after the last
+    selected one cannot change the result and are not run."""
+    B, T = tokens.shape
+    d = sd["decoder.ln.weight"].shape[0]
+    x = sd["decoder.token_embedding.weight"][tokens] + sd["decoder.positional_embedding"][:T]
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))[None, None]
+    last = max(l for l, _ in heads)
+    cap_q, cap_k = {}, {}
+    for l in range(min(n_layer, last + 1)):
+        p = f"decoder.blocks.{l}"
+        h = _ln(x, sd, p + ".attn_ln")
+        q = F.linear(h, sd[p + ".attn.query.weight"], sd[p + ".attn.query.bias"]).view(B, T, n_head, HEAD_DIM)
+        k = F.linear(h, sd[p + ".attn.key.weight"]).view(B, T, n_head, HEAD_DIM)
+        v = F.linear(h, sd[p + ".attn.value.weight"], sd[p + ".attn.value.bias"]).view(B, T, n_head, HEAD_DIM)
+        x = x + F.linear(_attend(q, k, v, causal).reshape(B, T, d), sd[p + ".attn.out.weight"], sd[p + ".attn.out.bias"])
+        h = _ln(x, sd, p + ".cross_attn_ln")
+        q = F.linear(h, sd[p + ".cross_attn.query.weight"], sd[p + ".cross_attn.query.bias"])
+        k = F.linear(xa, sd[p + ".cross_attn.key.weight"])
+        v = F.linear(xa, sd[p + ".cross_attn.value.weight"], sd[p + ".cross_attn.value.bias"])
+        cap_q[l], cap_k[l] = q, k
+        Ta = xa.shape[1]
+        a = _attend(q.view(B, T, n_head, HEAD_DIM), k.view(B, Ta, n_head, HEAD_DIM), v.view(B, Ta, n_head, HEAD_DIM))
+        x = x + F.linear(a.reshape(B, T, d), sd[p + ".cross_attn.out.weight"], sd[p + ".cross_attn.out.bias"])
+        x = x + _mlp(_ln(x, sd, p + ".mlp_ln"), sd, p)
+    scale = HEAD_DIM ** -0.25
+    out = []
+    for l, hd in heads:
+        qh = cap_q[l].view(B, T, n_head, HEAD_DIM)[:, :, hd].float() * scale
+        kh = cap_k[l].view(B, -1, n_head, HEAD_DIM)[:, :, hd].float() * scale
+        out.append(qh @ kh.transpose(-1, -2))
+    return torch.stack(out, 1)
+
+
+def median_filter7(x: torch.Tensor, width: int = 7) -> torch.Tensor:
+    """Median along the last dim with reflect padding (dtw_align.py:65-84)."""
+    pad = width // 2
+    if x.shape[-1] <= pad:
+        return x
+    flat = F.pad(x.reshape(-1, 1, x.shape[-1]), (pad, pad), mode="reflect")
+    return flat.unfold(-1, width, 1).sort(dim=-1).values[..., width // 2].reshape(x.shape)
+
+
+def align_prep(weights: torch.Tensor, actual_lens: list[int], audio_caps: list[int], medfilt_width: int = 7) -> torch.Tensor:
+    """``_dtw_prep_batch`` (dtw_align.py:700-753): columns at or past a chunk's audio cap are masked out of
+    the softmax, mean / variance over the chunk's valid text rows per (head, audio column), normalise with
+    std = sqrt(max(var, 1e-12)), median filter along audio over the full width, mean over heads.
+    weights f32 [B, H, T, Ta] -> f32 [B, T, max(audio_caps)]."""
+    B, H, T, Ta = weights.shape
+    lens = torch.tensor(actual_lens)
+    caps = torch.tensor(audio_caps)
+    audio_mask = torch.arange(Ta)[None, :] < caps[:, None]
+    w = weights.masked_fill(~audio_mask[:, None, None, :], float("-inf"))
+    w = torch.softmax(w, dim=-1)
+    tm = (torch.arange(T)[None, :] < lens[:, None])[:, None, :, None].to(w.dtype)
+    n = lens.view(B, 1, 1, 1).to(w.dtype)
+    mean = (w * tm).sum(dim=-2, keepdim=True) / n
+    var = (((w - mean) ** 2) * tm).sum(dim=-2, keepdim=True) / n
+    w = (w - mean) / var.clamp_min(1e-12).sqrt()
+    if medfilt_width > 1:
+        w = median_filter7(w, medfilt_width)
+    return w.mean(dim=1)[:, :, : int(caps.max())].contiguous()
+
+
+def dtw_path(x: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """``_dtw_numba`` (dtw_align.py:170-223): cost[i, j] = x[i-1, j-1] + min(diagonal, up, left) in float32
+    with ties resolved diagonal, then up (text index), then left (time index); backtrace from (N, M) with
+    the borders forcing 'left' on row 0 and 'up' on column 0.  Evaluated one anti-diagonal at a time.
+    Returns (text_idx, time_idx) int64, both of the path length."""
+    x = np.asarray(x, dtype=np.float32)
+    N, M = x.shape
+    cost = np.full((N + 1, M + 1), np.inf, dtype=np.float32)
+    trace = np.full((N + 1, M + 1), -1, dtype=np.int8)
+    trace[0, :] = 2
+    trace[:, 0] = 1
+    trace[0, 0] = -1
+    cost[0, 0] = 0.0
+    for k in range(2, N + M + 1):
+        i = np.arange(max(1, k - M), min(N, k - 1) + 1)
+        j = k - i
+        c0, c1, c2 = cost[i - 1, j - 1], cost[i - 1, j], cost[i, j - 1]
+        t = np.where((c0 <= c1) & (c0 <= c2), 0, np.where(c1 <= c2, 1, 2)).astype(np.int8)
+        c = np.where(t == 0, c0, np.where(t == 1, c1, c2))
+        cost[i, j] = x[i - 1, j - 1] + c
+        trace[i, j] = t
+    i, j = N, M
+    ti, tj = [], []
+    while i > 0 or j > 0:
+        ti.append(i - 1)
+        tj.append(j - 1)
+        t = trace[i, j]
+        if t == 0:
+            i, j = i - 1, j - 1
+        elif t == 1:
+            i -= 1
+        else:
+            j -= 1
+    return np.array(ti[::-1], dtype=np.int64), np.array(tj[::-1], dtype=np.int64)
