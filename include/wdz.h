@@ -252,6 +252,39 @@ int wdz_reargmax(wdz_engine* e, const int32_t* rows_dev, const wdz_rule_desc* ru
 int wdz_rules_argmax(wdz_engine* e, const float* logits_dev, const wdz_rule_desc* rules_dev, int n,
                      int apply_penalty, int32_t* out_dev, wdz_stream s);
 
+/* ---- word-timing alignment (the step after decode of every finished window) ----
+ * Device steps of fill_word_timings_batch (src/whisperdrz/dtw_align.py:1112-1240); text parsing and
+ * re-rendering stay host code on the caller's side.
+ *
+ * wdz_align_configure: the (layer, head) pairs whose cross-attention tracks time; replaces the head mask
+ * of make_head_mask (dtw_align.py:52-62).  layer_head_pairs is host int32 [n_heads][2], n_heads <= 16. */
+int wdz_align_configure(wdz_engine* e, const int32_t* layer_head_pairs, int n_heads);
+/* Most chunks of t_pad tokens one wdz_align_matrix call takes (its scratch is the idle encoder workspace). */
+int wdz_align_capacity(wdz_engine* e, int t_pad);
+/* Replaces model.decoder(full_tokens, xa_batch) under CrossAttnCapture, compute_attention and
+ * _dtw_prep_batch (dtw_align.py:1181-1195, 498-586, 700-753).  Chunk b holds chunk_lens_dev[b] tokens
+ * (sot sequence, no-timestamps, ids, eot) at tokens_dev[b * t_pad ...], eot-padded, and is aligned against
+ * the audio window whose cross keys sit in slot chunk_slots_dev[b] (written by wdz_cross_kv / wdz_prefill).
+ * Runs the decoder teacher-forced up to the last configured layer, takes QK^T of the configured heads
+ * against the cached cross keys, softmax over the audio columns below audio_caps_dev[b], normalises each
+ * (head, column) over the chunk's rows, median-filters (width 7, reflect) along audio and averages the
+ * heads.  matrix_out_dev: f32 [n_chunks][t_pad][n_audio_ctx], rows past a chunk's length zero.
+ * The pass writes the self-attention rows of the chunks' slots from position 0 (their decoded window is
+ * finished) and resets those slots' lengths; slots of one call must be distinct. */
+int wdz_align_matrix(wdz_engine* e, const int32_t* tokens_dev, const int32_t* chunk_lens_dev,
+                     const int32_t* chunk_slots_dev, const int32_t* audio_caps_dev, int n_chunks, int t_pad,
+                     float* matrix_out_dev, wdz_stream s);
+/* Replaces _dtw_numba on the negated matrix with the anchor bands of _apply_anchor_bands
+ * (dtw_align.py:170-223, 589-641).  Chunk b's cost is -matrix[b * chunk_stride + (row0[b] + i) * ld + j]
+ * for i < n_rows[b], j < n_cols[b], and +inf where j is outside [col_lo[b][i], col_hi[b][i])
+ * (int32 [n_chunks][limit_stride]; both NULL = no limits).  Outputs the monotonic minimum-cost path from
+ * (0, 0) to the last cell: text_idx / time_idx int32 [n_chunks][max_rows + max_cols] in forward order and
+ * its length.  max_rows <= 511 and max_rows * max_cols / 4 within one CTA's shared memory (~200 KB). */
+int wdz_dtw(wdz_engine* e, const float* matrix_dev, int64_t chunk_stride, int64_t ld, const int32_t* row0_dev,
+            const int32_t* n_rows_dev, const int32_t* n_cols_dev, const int32_t* col_lo_dev, const int32_t* col_hi_dev,
+            int limit_stride, int n_chunks, int max_rows, int max_cols, int32_t* text_idx_out_dev,
+            int32_t* time_idx_out_dev, int32_t* path_len_out_dev, wdz_stream s);
+
 #ifdef __cplusplus
 }
 #endif

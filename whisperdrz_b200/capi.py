@@ -80,6 +80,10 @@ SYMBOLS = {
     "wdz_ts_tokens": (I, [P, I, P, I, P]),
     "wdz_reargmax": (I, [P, P, P, I, P, P]),
     "wdz_rules_argmax": (I, [P, P, P, I, I, P, P]),
+    "wdz_align_configure": (I, [P, P, I]),
+    "wdz_align_capacity": (I, [P, I]),
+    "wdz_align_matrix": (I, [P, P, P, P, P, I, I, P, P]),
+    "wdz_dtw": (I, [P, P, I64, I64, P, P, P, P, P, I, I, I, I, P, P, P, P]),
 }
 
 _lib = None

@@ -23,6 +23,7 @@
 #include "gemv_mma.cuh"
 #include "logmel.cuh"
 #include "rules.cuh"
+#include "align.cuh"
 #ifdef WDZ_WITH_TC
 #include "gemm_tc.cuh"
 #include "attn_tc.cuh"
@@ -80,6 +81,10 @@ struct wdz_engine {
   float *dx = nullptr, *dxn = nullptr, *dqkv = nullptr, *dao = nullptr, *dq = nullptr, *dh = nullptr;
   float *part_o = nullptr, *part_ml = nullptr, *logits = nullptr;
   int* dpos = nullptr;
+  int* al_slots = nullptr;     // rows of a teacher-forced alignment pass
+  int* al_pos = nullptr;
+  AlignHeads al_heads{};       // (layer, head) pairs of wdz_align_configure
+  int al_last_layer = -1;
   DevStatus* status = nullptr;
   int64_t part_entries = 0;
   int max_emit = 0;
@@ -191,6 +196,8 @@ size_t carve(wdz_engine* e, char* base) {
   e->dq = (float*)take(sizeof(float) * R * dt);
   e->dh = (float*)take(sizeof(float) * R * 4 * dt);
   e->dpos = (int*)take(sizeof(int) * R);
+  e->al_slots = (int*)take(sizeof(int) * R);
+  e->al_pos = (int*)take(sizeof(int) * R);
   e->g_tokens = (int*)take(sizeof(int) * (R + 8));
   e->g_slots = (int*)take(sizeof(int) * (R + 8));
   e->g_next = (int*)take(sizeof(int) * (R + 8));
@@ -453,12 +460,17 @@ GemvMmaParams mma_params(const void* x, int64_t ldx, const void* W, const void* 
   return p;
 }
 
+struct AlignCapture {   // teacher-forced alignment pass: keep the alignment heads' cross queries, stop after the last
+  float* qcap; int64_t rows_total, row_base;
+};
+
 // tokens/slots/positions: device int32 [n].  Logits of the emit rows land in e->logits.
 // Activations between kernels (LayerNorm output, attention output, MLP hidden)
 // are stored in T; the residual stream, q/k/v of the new rows and the logits stay fp32.
+
 template <typename T>
 int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const int* positions, int n,
-                      const int* emit_rows, int n_emit, cudaStream_t s) {
+                      const int* emit_rows, int n_emit, cudaStream_t s, const AlignCapture* cap = nullptr) {
   constexpr bool kBf16 = sizeof(T) == 2;
   const wdz_config& c = e->cfg;
   const int d = c.n_text_state;
@@ -515,6 +527,16 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
 
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s))) return rc;
     if ((rc = gemm(EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, w.xout_w, wb))) return rc;
+    if (cap) {
+      int here = 0;
+      for (int j = 0; j < e->al_heads.n; ++j) here += e->al_heads.layer[j] == l;
+      if (here > 0) {
+        align_capture_kernel<<<n, 64 * here, 0, s>>>(e->dq, d, n, l, e->al_heads, cap->qcap, cap->rows_total, cap->row_base);
+        e->launches += 1;
+        WDZ_LAUNCH_CHECK(e, "align_capture");
+      }
+      if (l >= e->al_last_layer) return WDZ_OK;   // later layers cannot change the captured queries
+    }
     ap.q = e->dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
     ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
     if ((rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
@@ -874,6 +896,10 @@ int wdz_finalize(wdz_engine* e) {
         return e->fail(WDZ_ECUDA, "attn_dec_stream smem attribute: %s", cudaGetErrorString(ce2));
       }
     }
+  }
+  if (cudaFuncSetAttribute(dtw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+    cudaError_t ce3 = cudaGetLastError();
+    return e->fail(WDZ_ECUDA, "dtw smem attribute: %s", cudaGetErrorString(ce3));
   }
   if (c.dtype == WDZ_BF16 && c.n_text_state % 256)
     return e->fail(WDZ_EINVAL, "the bf16 decoder needs n_text_state to be a multiple of 256 (got %d)", c.n_text_state);
@@ -1375,6 +1401,123 @@ int wdz_rules_argmax(wdz_engine* e, const float* logits_dev, const wdz_rule_desc
   if (rc) return rc;
   if (!logits_dev || !out_dev || n < 0) return e->fail(WDZ_EINVAL, "wdz_rules_argmax: null argument");
   return rules_launch(e, logits_dev, nullptr, rules_dev, n, apply_penalty ? 1 : 0, out_dev, (cudaStream_t)s);
+}
+
+// ---- word-timing alignment -------------------------------------------------
+int wdz_align_configure(wdz_engine* e, const int32_t* layer_head_pairs, int n_heads) {
+  if (!e) return WDZ_EINVAL;
+  if (!layer_head_pairs || n_heads < 1 || n_heads > ALIGN_MAX_HEADS)
+    return e->fail(WDZ_EINVAL, "wdz_align_configure: 1..%d (layer, head) pairs", ALIGN_MAX_HEADS);
+  if (e->cfg.n_text_state / e->cfg.n_text_head != ALIGN_HD)
+    return e->fail(WDZ_EINVAL, "wdz_align_configure: head size %d is not supported", e->cfg.n_text_state / e->cfg.n_text_head);
+  AlignHeads h{};
+  int last = -1;
+  for (int j = 0; j < n_heads; ++j) {
+    const int l = layer_head_pairs[2 * j], hd = layer_head_pairs[2 * j + 1];
+    if (l < 0 || l >= e->cfg.n_text_layer || hd < 0 || hd >= e->cfg.n_text_head)
+      return e->fail(WDZ_EINVAL, "wdz_align_configure: pair %d = (%d, %d) is outside the decoder", j, l, hd);
+    h.layer[j] = l; h.head[j] = hd;
+    if (l > last) last = l;
+  }
+  h.n = n_heads;
+  e->al_heads = h;
+  e->al_last_layer = last;
+  return WDZ_OK;
+}
+
+// Scratch of the alignment lives in encoder activations that are idle between encoder calls: the scores
+// [chunks, heads, t_pad, Ta] f32 in the MLP hidden buffer, queries and column statistics in the QKV buffer.
+static int64_t align_capacity(const wdz_engine* e, int t_pad) {
+  const wdz_config& c = e->cfg;
+  if (e->al_heads.n < 1 || t_pad < 1) return 0;
+  const int64_t hid_bytes = (int64_t)e->esz * c.max_clips * c.n_audio_ctx * 4 * c.n_audio_state;
+  const int64_t qkv_bytes = (int64_t)e->esz * c.max_clips * c.n_audio_ctx * 3 * c.n_audio_state;
+  const int64_t per_w = (int64_t)e->al_heads.n * t_pad * c.n_audio_ctx * 4;
+  const int64_t per_q = (int64_t)e->al_heads.n * t_pad * ALIGN_HD * 4 + (int64_t)e->al_heads.n * c.n_audio_ctx * 8 + 512;
+  const int64_t a = hid_bytes / per_w, b = qkv_bytes / per_q;
+  return a < b ? a : b;
+}
+
+int wdz_align_capacity(wdz_engine* e, int t_pad) {
+  if (!e) return WDZ_EINVAL;
+  const int64_t n = align_capacity(e, t_pad);
+  return n > (1 << 20) ? (1 << 20) : (int)n;
+}
+
+int wdz_align_matrix(wdz_engine* e, const int32_t* tokens_dev, const int32_t* chunk_lens_dev,
+                     const int32_t* chunk_slots_dev, const int32_t* audio_caps_dev, int n_chunks, int t_pad,
+                     float* matrix_out_dev, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  const wdz_config& c = e->cfg;
+  if (!tokens_dev || !chunk_lens_dev || !chunk_slots_dev || !audio_caps_dev || !matrix_out_dev || n_chunks < 0)
+    return e->fail(WDZ_EINVAL, "wdz_align_matrix: null argument");
+  if (e->al_heads.n < 1) return e->fail(WDZ_ESTATE, "wdz_align_matrix: wdz_align_configure has not been called");
+  if (n_chunks == 0) return WDZ_OK;
+  if (t_pad < 1 || t_pad > c.max_tokens || t_pad > c.n_text_ctx)
+    return e->fail(WDZ_ECAPACITY, "wdz_align_matrix: %d tokens per chunk > %d", t_pad, c.max_tokens < c.n_text_ctx ? c.max_tokens : c.n_text_ctx);
+  if (c.n_audio_ctx > 32 * ALIGN_COLS_PER_LANE)
+    return e->fail(WDZ_ECAPACITY, "wdz_align_matrix: %d audio positions > %d", c.n_audio_ctx, 32 * ALIGN_COLS_PER_LANE);
+  if (n_chunks > align_capacity(e, t_pad))
+    return e->fail(WDZ_ECAPACITY, "wdz_align_matrix: %d chunks of %d tokens > %lld per call (wdz_align_capacity)", n_chunks,
+                   t_pad, (long long)align_capacity(e, t_pad));
+  cudaStream_t st = (cudaStream_t)s;
+  const int64_t rows = (int64_t)n_chunks * t_pad;
+  const int nh = e->al_heads.n, Ta = c.n_audio_ctx;
+  float* w = (float*)e->hid;
+  float* qcap = (float*)e->qkv;
+  float* mean = qcap + (int64_t)nh * rows * ALIGN_HD;
+  float* rstd = mean + (int64_t)n_chunks * nh * Ta;
+  // the pass overwrites the self-attention rows of the chunks' slots from position 0
+  reset_seqlens_kernel<<<(n_chunks + 255) / 256, 256, 0, st>>>(chunk_slots_dev, e->seq_lens, n_chunks, c.n_slots);
+  for (int64_t r0 = 0; r0 < rows; r0 += c.max_rows) {
+    const int n = (int)(rows - r0 < c.max_rows ? rows - r0 : c.max_rows);
+    align_rows_kernel<<<(n + 255) / 256, 256, 0, st>>>(chunk_slots_dev, chunk_lens_dev, t_pad, (int)r0, n, c.n_slots, e->al_slots, e->al_pos);
+    e->launches += 1;
+    AlignCapture cap{qcap, rows, r0};
+    rc = c.dtype == WDZ_BF16
+             ? forward_rows_impl<bf16>(e, tokens_dev + r0, e->al_slots, e->al_pos, n, nullptr, 0, st, &cap)
+             : forward_rows_impl<float>(e, tokens_dev + r0, e->al_slots, e->al_pos, n, nullptr, 0, st, &cap);
+    if (rc) return rc;
+  }
+  const dim3 gs((t_pad + 7) / 8, nh, n_chunks);
+  if (c.dtype == WDZ_BF16)
+    align_scores_kernel<bf16><<<gs, 256, 0, st>>>(qcap, rows, t_pad, chunk_lens_dev, chunk_slots_dev, audio_caps_dev, e->al_heads,
+                                                  (const bf16*)e->cross_k, c.n_slots, Ta, c.n_text_state, w);
+  else
+    align_scores_kernel<float><<<gs, 256, 0, st>>>(qcap, rows, t_pad, chunk_lens_dev, chunk_slots_dev, audio_caps_dev, e->al_heads,
+                                                   (const float*)e->cross_k, c.n_slots, Ta, c.n_text_state, w);
+  align_colstats_kernel<<<dim3((Ta + 127) / 128, nh, n_chunks), 128, 0, st>>>(w, nh, t_pad, Ta, chunk_lens_dev, mean, rstd);
+  align_matrix_kernel<<<dim3(t_pad, n_chunks), 256, 0, st>>>(w, mean, rstd, nh, t_pad, Ta, chunk_lens_dev, matrix_out_dev);
+  e->launches += 4;
+  WDZ_LAUNCH_CHECK(e, "align_matrix");
+  return WDZ_OK;
+}
+
+int wdz_dtw(wdz_engine* e, const float* matrix_dev, int64_t chunk_stride, int64_t ld, const int32_t* row0_dev,
+            const int32_t* n_rows_dev, const int32_t* n_cols_dev, const int32_t* col_lo_dev, const int32_t* col_hi_dev,
+            int limit_stride, int n_chunks, int max_rows, int max_cols, int32_t* text_idx_out_dev,
+            int32_t* time_idx_out_dev, int32_t* path_len_out_dev, wdz_stream s) {
+  int rc = check_ready(e);
+  if (rc) return rc;
+  if (!matrix_dev || !row0_dev || !n_rows_dev || !n_cols_dev || !text_idx_out_dev || !time_idx_out_dev ||
+      !path_len_out_dev || n_chunks < 0 || (!col_lo_dev) != (!col_hi_dev))
+    return e->fail(WDZ_EINVAL, "wdz_dtw: null argument");
+  if (n_chunks == 0) return WDZ_OK;
+  if (max_rows < 1 || max_cols < 1 || max_rows > 511 || dtw_smem_bytes(max_rows, max_cols) > (size_t)200 * 1024)
+    return e->fail(WDZ_ECAPACITY, "wdz_dtw: %d x %d cells do not fit one CTA's shared memory (rows <= 511, rows x cols / 4 <= ~200 KB)",
+                   max_rows, max_cols);
+  if (col_lo_dev && limit_stride < max_rows) return e->fail(WDZ_EINVAL, "wdz_dtw: limit_stride %d < max_rows %d", limit_stride, max_rows);
+  DtwParams p{};
+  p.mat = matrix_dev; p.chunk_stride = chunk_stride; p.ld = ld;
+  p.row0 = row0_dev; p.n_rows = n_rows_dev; p.n_cols = n_cols_dev;
+  p.col_lo = col_lo_dev; p.col_hi = col_hi_dev; p.limit_stride = limit_stride;
+  p.max_rows = max_rows; p.max_cols = max_cols; p.path_cap = max_rows + max_cols;
+  p.text_idx = text_idx_out_dev; p.time_idx = time_idx_out_dev; p.path_len = path_len_out_dev;
+  dtw_kernel<<<n_chunks, 512, dtw_smem_bytes(max_rows, max_cols), (cudaStream_t)s>>>(p);
+  e->launches += 1;
+  WDZ_LAUNCH_CHECK(e, "dtw");
+  return WDZ_OK;
 }
 
 }  // extern "C"

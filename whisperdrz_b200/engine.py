@@ -408,3 +408,66 @@ class Engine:
         self._check(self.lib.wdz_rules_argmax(self.h, logits.data_ptr(), None if rd is None else rd.data_ptr(),
                                               logits.shape[0], int(penalty), out.data_ptr(), self._stream()))
         return out
+
+    # ------------------------------------------------------- word-timing alignment
+    def align_configure(self, heads) -> None:
+        """(layer, head) pairs whose cross-attention tracks time (dtw_align.py:52-62)."""
+        arr = np.ascontiguousarray(np.asarray(heads, dtype=np.int32).reshape(-1, 2))
+        self._check(self.lib.wdz_align_configure(self.h, arr.ctypes.data, arr.shape[0]))
+        self.align_heads = [tuple(int(v) for v in r) for r in arr]
+
+    def align_capacity(self, t_pad: int) -> int:
+        return int(self.lib.wdz_align_capacity(self.h, int(t_pad)))
+
+    def align_matrix(self, tokens, lens, slots, audio_caps) -> torch.Tensor:
+        """tokens int [B, T] (``alignment.build_full_tokens``), lens / slots / audio_caps [B] ->
+        f32 [B, T, n_audio_ctx] on the device: the cost matrix before negation, rows past a chunk's length
+        zero (dtw_align.py:1181-1195).  Slots must be distinct; more chunks than one call takes are run
+        in several calls."""
+        tok = torch.as_tensor(np.asarray(tokens), dtype=torch.int32)
+        B, T = tok.shape
+        if len(set(int(s) for s in slots)) != B:
+            raise ValueError("align_matrix: the chunks of one call must sit in distinct slots")
+        out = torch.empty(B, T, self.dims.n_audio_ctx, dtype=torch.float32, device=self.device)
+        cap = self.align_capacity(T)
+        if cap < 1:
+            raise capi.WdzError(-5, f"no room to align chunks of {T} tokens (configure heads first)")
+        tok_d = tok.to(self.device)
+        lens_d, slots_d, caps_d = self._i32(lens), self._i32(slots), self._i32(audio_caps)
+        for b0 in range(0, B, cap):
+            n = min(cap, B - b0)
+            self._check(self.lib.wdz_align_matrix(
+                self.h, tok_d[b0:b0 + n].contiguous().data_ptr(), lens_d[b0:].data_ptr(), slots_d[b0:].data_ptr(),
+                caps_d[b0:].data_ptr(), n, T, out[b0:].data_ptr(), self._stream()))
+        return out
+
+    def dtw(self, matrix: torch.Tensor, row0, n_rows, n_cols, limits=None):
+        """Minimum-cost monotonic paths through ``-matrix[b, row0[b] : row0[b] + n_rows[b], : n_cols[b]]``
+        (dtw_align.py:170-223).  ``limits`` = per chunk (lo, hi) int arrays [n_rows[b]]: columns outside
+        [lo, hi) of a row cost +inf (anchor bands, dtw_align.py:589-641).  Returns [(text_idx, time_idx)]
+        as int64 numpy arrays."""
+        matrix = matrix.to(device=self.device, dtype=torch.float32)
+        if matrix.dim() == 2:
+            matrix = matrix[None]
+        matrix = matrix.contiguous()
+        B = matrix.shape[0]
+        max_rows, max_cols = max(1, max(n_rows)), max(1, max(n_cols))
+        lo_d = hi_d = None
+        if limits is not None:
+            lo = np.zeros((B, max_rows), dtype=np.int32)
+            hi = np.zeros((B, max_rows), dtype=np.int32)
+            for b, (l, h) in enumerate(limits):
+                lo[b, : len(l)] = l
+                hi[b, : len(h)] = h
+            lo_d, hi_d = torch.from_numpy(lo).to(self.device), torch.from_numpy(hi).to(self.device)
+        cap = max_rows + max_cols
+        ti = torch.empty(B, cap, dtype=torch.int32, device=self.device)
+        tj = torch.empty(B, cap, dtype=torch.int32, device=self.device)
+        ln = torch.empty(B, dtype=torch.int32, device=self.device)
+        self._check(self.lib.wdz_dtw(
+            self.h, matrix.data_ptr(), matrix.stride(0), matrix.stride(1), self._i32(row0).data_ptr(),
+            self._i32(n_rows).data_ptr(), self._i32(n_cols).data_ptr(),
+            None if lo_d is None else lo_d.data_ptr(), None if hi_d is None else hi_d.data_ptr(), max_rows, B,
+            max_rows, max_cols, ti.data_ptr(), tj.data_ptr(), ln.data_ptr(), self._stream()))
+        ti_h, tj_h, ln_h = ti.cpu().numpy(), tj.cpu().numpy(), ln.cpu().numpy()
+        return [(ti_h[b, : ln_h[b]].astype(np.int64), tj_h[b, : ln_h[b]].astype(np.int64)) for b in range(B)]
