@@ -114,3 +114,35 @@ def test_align_chunks_end_to_end_word_times(gold):
         assert np.allclose(np.array(times[bi]), gold[f"word_times{bi}"], atol=0.0201), (times[bi], gold[f"word_times{bi}"])
     assert times[2] == times[0]
     e.close()
+
+
+def test_tensor_core_pass_matches_row_wise_pass_on_long_chunks(gold):
+    """bf16, chunks of 300 and 170 tokens: with room for whole chunks in one forward call the pass runs its
+    attention on tcgen05 (several 128-query tiles, causal diagonal tiles, ragged lengths); with max_rows
+    below the chunk length it falls back to the row-wise decode kernels.  Same matrices up to bf16 noise,
+    and both close to the fp32 oracle."""
+    from whisperdrz_b200.engine import Engine
+    dims = ModelDimensions.from_name("test-small")
+    sd = init_state_dict(dims, 0)
+    rng = np.random.RandomState(11)
+    ids = [rng.randint(0, 50000, size=295).tolist(), rng.randint(0, 50000, size=165).tolist()]
+    tokens, lens = A.build_full_tokens(ids)
+    caps = [1500, 1100]
+    slots = [1, 2]
+    out = []
+    xa_keep = None
+    for max_rows in (320, 64):
+        e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=4, max_clips=2, max_rows=max_rows)
+        xa_keep = _setup(e, gold, slots)
+        out.append(e.align_matrix(tokens, lens, slots, caps).cpu())
+        e.device_status()
+        e.close()
+    for b in range(2):
+        a, c = out[0][b, : lens[b]], out[1][b, : lens[b]]
+        assert (a - c).abs().max() < 0.15 and (a - c).abs().mean() < 0.01, (float((a - c).abs().max()), float((a - c).abs().mean()))
+    heads = [tuple(int(v) for v in h) for h in gold["heads"]]
+    w = oracle.align_scores(sd, torch.from_numpy(tokens).long(), xa_keep.float().cpu(), dims.n_text_layer, dims.n_text_head, heads)
+    m = oracle.align_prep(w, lens, caps)
+    for b in range(2):
+        diff = (out[0][b, : lens[b], : max(caps)] - m[b, : lens[b]]).abs()
+        assert diff.mean() < 0.02 and diff.max() < 0.5, (float(diff.mean()), float(diff.max()))

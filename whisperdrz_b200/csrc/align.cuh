@@ -15,6 +15,7 @@
 //                          anchor bands as an allowed column range per row (_apply_anchor_bands :589-641)
 #pragma once
 #include "common.cuh"
+#include "../../include/wdz.h"
 
 namespace wdz {
 
@@ -212,6 +213,7 @@ struct DtwParams {
   const int* col_lo; const int* col_hi; int limit_stride;     // nullptr: no limits
   int max_rows, max_cols, path_cap;
   int* text_idx; int* time_idx; int* path_len;
+  DevStatus* status;
 };
 
 __global__ void __launch_bounds__(512) dtw_kernel(DtwParams p) {
@@ -220,8 +222,13 @@ __global__ void __launch_bounds__(512) dtw_kernel(DtwParams p) {
   const int N = min(max(p.n_rows[b], 0), p.max_rows), M = min(max(p.n_cols[b], 0), p.max_cols);
   int* tout = p.text_idx + (int64_t)b * p.path_cap;
   int* jout = p.time_idx + (int64_t)b * p.path_cap;
-  if (N == 0 || M == 0) {
-    if (threadIdx.x == 0) p.path_len[b] = 0;
+  // a chunk whose rows or columns would leave its slab of the matrix is refused, not read
+  const bool bad = p.row0[b] < 0 || M > p.ld || (p.chunk_stride > 0 && (int64_t)(p.row0[b] + N) * p.ld > p.chunk_stride);
+  if (N == 0 || M == 0 || bad) {
+    if (threadIdx.x == 0) {
+      p.path_len[b] = 0;
+      if (bad && p.status) atomicCAS(&p.status->code, 0, WDZ_EINVAL);
+    }
     return;
   }
   const int rowbytes = (M + 3) >> 2;
@@ -237,7 +244,10 @@ __global__ void __launch_bounds__(512) dtw_kernel(DtwParams p) {
   int lo = 0, hi = M;
   if (i >= 1 && i <= N) {
     mrow = p.mat + (int64_t)b * p.chunk_stride + (int64_t)(p.row0[b] + i - 1) * p.ld;
-    if (p.col_lo) { lo = p.col_lo[(int64_t)b * p.limit_stride + i - 1]; hi = p.col_hi[(int64_t)b * p.limit_stride + i - 1]; }
+    if (p.col_lo) {
+      lo = max(p.col_lo[(int64_t)b * p.limit_stride + i - 1], 0);
+      hi = min(p.col_hi[(int64_t)b * p.limit_stride + i - 1], M);
+    }
   }
   auto xval = [&](int j) -> float {   // j = 1..M
     const int c = j - 1;

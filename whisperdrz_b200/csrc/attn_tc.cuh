@@ -1,5 +1,8 @@
-// Encoder self-attention on tcgen05 (non-causal, head_dim 64, bf16 in, fp32
-// softmax): MultiHeadAttention.qkv_attention, src/whisperdrz/model.py:276-298.
+// Many-query attention on tcgen05 (head_dim 64, bf16 in, fp32 softmax):
+// MultiHeadAttention.qkv_attention, src/whisperdrz/model.py:276-298.  Used for
+// the encoder's self-attention (Q, K, V columns of one [B, T, 3d] tensor) and
+// for the teacher-forced alignment pass of the decoder, where the queries of a
+// chunk attend to its slot's cross cache, or causally to its self cache.
 //
 // One CTA per (128-query tile, head, window); two CTAs share an SM so that one
 // CTA's softmax overlaps the other's MMAs.  Per 128-key tile:
@@ -32,8 +35,14 @@ constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KT
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(QT >> 4) << 24);
 
 struct AttnTcParams {
-  bf16* out;            // [B * T, d]
-  int T, d, n_kv;       // n_kv = ceil(T / 128)
+  bf16* out;            // row (b * out_rows + q) holds query q of batch b, d columns
+  int out_rows, d;
+  int Tq, Tk;           // queries / keys per batch entry when no lengths are given
+  const int* lens;      // optional [batches]: valid queries (and, if causal, keys) of a batch entry
+  const int* kv_z;      // optional [batches]: third coordinate of the K / V maps (a cache slot); < 0 skips the batch
+  int kv_z_base, kv_z_limit;   // added to kv_z[b] (layer * slots); slots
+  int q_col0, k_col0, v_col0;  // first column of head 0 in the Q / K / V maps
+  int causal;           // key k visible to query q only if k <= q
   DevStatus* status;
 };
 
@@ -89,7 +98,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 
 __global__ void __launch_bounds__(192, 2)
-attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams p) {
+attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* q_s = smem;
@@ -107,6 +117,18 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * QT, h = blockIdx.y, b = blockIdx.z;
+  // uniform over the CTA: nothing to do for tiles past the batch entry's queries or for skipped entries
+  const int q_valid = p.lens ? min(p.lens[b], p.Tq) : p.Tq;
+  int kvz = b;
+  if (p.kv_z) {
+    const int z = p.kv_z[b];
+    if (z < 0 || z >= p.kv_z_limit) return;
+    kvz = p.kv_z_base + z;
+  }
+  if (q0 >= q_valid) return;
+  const int k_valid = p.causal ? min(q_valid, p.Tk) : p.Tk;          // keys that exist
+  const int k_end = p.causal ? min(k_valid, q0 + QT) : k_valid;      // keys this tile can see
+  const int n_kv = (k_end + KT - 1) / KT;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < KV_STAGES; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
@@ -116,7 +138,9 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
     mbar_init(pv_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmQKV) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmQ) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmK) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmV) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -130,22 +154,22 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_3d(q_s, &tmQKV, q_full, h * 64, q0, b);
-      for (int j = 0; j < p.n_kv; ++j) {
+      tma_load_3d(q_s, &tmQ, q_full, p.q_col0 + h * 64, q0, b);
+      for (int j = 0; j < n_kv; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t phase = (j / KV_STAGES) & 1;
         if (!mbar_wait(kv_empty + st, phase ^ 1, abort_flag, p.status)) break;
         uint8_t* k_dst = kv_s + st * 2 * TILE_BYTES;
         mbar_expect_tx(kv_full + st, 2 * TILE_BYTES);
-        tma_load_3d(k_dst, &tmQKV, kv_full + st, p.d + h * 64, j * KT, b);
-        tma_load_3d(k_dst + TILE_BYTES, &tmQKV, kv_full + st, 2 * p.d + h * 64, j * KT, b);
+        tma_load_3d(k_dst, &tmK, kv_full + st, p.k_col0 + h * 64, j * KT, kvz);
+        tma_load_3d(k_dst + TILE_BYTES, &tmV, kv_full + st, p.v_col0 + h * 64, j * KT, kvz);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
       const uint32_t q_addr = smem_u32(q_s);
-      for (int j = 0; ok && j < p.n_kv; ++j) {
+      for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j % KV_STAGES;
         if (!(ok = mbar_wait(kv_full + st, (j / KV_STAGES) & 1, abort_flag, p.status))) break;
         if (!(ok = mbar_wait(s_empty, (j & 1) ^ 1, abort_flag, p.status))) break;
@@ -174,13 +198,15 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
 #pragma unroll
     for (int i = 0; i < 64; ++i) o[i] = 0.0f;
     bool ok = true;
-    for (int j = 0; j < p.n_kv; ++j) {
+    for (int j = 0; j < n_kv; ++j) {
       ok = mbar_wait(s_full, j & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const int k0 = j * KT;
-      const bool tail = k0 + KT > p.T;          // only the last key tile has columns past the sequence
+      // only the last key tile has columns past the sequence; under the causal rule also the diagonal tile
+      const bool tail = k0 + KT > k_valid || (p.causal && k0 + KT > q0);
+      const int k_lim = p.causal ? min(k_valid, q + 1) : k_valid;   // keys [0, k_lim) are visible to this row
       float mx = -INFINITY;
 #pragma unroll 1
       for (int hf = 0; hf < 2; ++hf) {
@@ -200,8 +226,8 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (k0 + hf * 64 + i < p.T) mx = fmaxf(mx, __uint_as_float(a[i]));
-            if (k0 + hf * 64 + 32 + i < p.T) mx = fmaxf(mx, __uint_as_float(b[i]));
+            if (k0 + hf * 64 + i < k_lim) mx = fmaxf(mx, __uint_as_float(a[i]));
+            if (k0 + hf * 64 + 32 + i < k_lim) mx = fmaxf(mx, __uint_as_float(b[i]));
           }
         }
       }
@@ -237,10 +263,10 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
           float p3 = ex2(fmaf(__uint_as_float(b[2 * i + 1]), QK_SCALE_LOG2E, -m_new));
           if (tail) {
             const int kk = k0 + hf * 64 + 2 * i;
-            if (kk >= p.T) p0 = 0.0f;
-            if (kk + 1 >= p.T) p1 = 0.0f;
-            if (kk + 32 >= p.T) p2 = 0.0f;
-            if (kk + 33 >= p.T) p3 = 0.0f;
+            if (kk >= k_lim) p0 = 0.0f;
+            if (kk + 1 >= k_lim) p1 = 0.0f;
+            if (kk + 32 >= k_lim) p2 = 0.0f;
+            if (kk + 33 >= k_lim) p3 = 0.0f;
           }
           sum += p0; sum1 += p1; sum2 += p2; sum3 += p3;
           pk[i] = pack_bf16(p0, p1);
@@ -257,18 +283,18 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnTcParams
       mbar_arrive(p_ready);
     }
     if (ok) {
-      ok = mbar_wait(pv_full, (p.n_kv - 1) & 1, abort_flag, p.status);
+      ok = mbar_wait(pv_full, (n_kv - 1) & 1, abort_flag, p.status);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after();
       const float inv = 1.0f / l;
-      bf16* dst = p.out + ((int64_t)b * p.T + q) * p.d + h * 64;
+      bf16* dst = p.out + ((int64_t)b * p.out_rows + q) * p.d + h * 64;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_ld32(lane_addr + COL_O + c * 32, v);
-        if (q < p.T) {
+        if (q < q_valid) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 t;

@@ -234,4 +234,19 @@ __global__ void zero_rows_kernel(T* __restrict__ p, int64_t bstride, int64_t row
   for (int i = threadIdx.x; i < d; i += blockDim.x) p[b * bstride + row_off + i] = from_f<T>(0.0f);
 }
 
+// f32 [n, ld_src] (first d columns) -> bf16 [n, ld_dst]; one block per row.
+__global__ void cast_rows_kernel(const float* __restrict__ src, int64_t ld_src, bf16* __restrict__ dst, int64_t ld_dst,
+                                 int n, int d) {
+  const int r = blockIdx.x;
+  if (r >= n) return;
+  for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)r * ld_src + c);
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(dst + (int64_t)r * ld_dst + c) = o;
+  }
+}
+
 }  // namespace wdz

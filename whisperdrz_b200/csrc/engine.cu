@@ -37,6 +37,9 @@ static int gemm_tc_init(wdz_engine* e);
 static int gemm_tc_launch(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s);
 static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& p, cudaStream_t s);
 static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int T, int d, int H, cudaStream_t s);
+static int attn_tc_chunks_launch(wdz_engine* e, const void* q, void* out, const void* cache_k, const void* cache_v,
+                                 int64_t S, int n_keys, int layer, const int* chunk_lens, const int* chunk_slots,
+                                 int n_chunks, int t_pad, bool causal, cudaStream_t s);
 #endif
 
 namespace {
@@ -462,6 +465,10 @@ GemvMmaParams mma_params(const void* x, int64_t ldx, const void* W, const void* 
 
 struct AlignCapture {   // teacher-forced alignment pass: keep the alignment heads' cross queries, stop after the last
   float* qcap; int64_t rows_total, row_base;
+  // tc_chunks > 0: the rows are tc_chunks whole chunks of t_pad tokens each, and attention runs on the tensor
+  // cores with a chunk's keys read once per 128 queries instead of once per query
+  int tc_chunks, t_pad;
+  const int* chunk_lens; const int* chunk_slots;
 };
 
 // tokens/slots/positions: device int32 [n].  Logits of the emit rows land in e->logits.
@@ -522,7 +529,20 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
     ap.layer = l;
     ap.q = e->dqkv; ap.ldq = 3 * d; ap.cache_k = e->self_k; ap.cache_v = e->self_v; ap.S = c.max_tokens;
     ap.positions = positions; ap.fixed_len = 0;
-    if ((rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
+    bool attn_done = false;
+#ifdef WDZ_WITH_TC
+    if constexpr (kBf16) {
+      if (cap && cap->tc_chunks > 0) {
+        cast_rows_kernel<<<n, 256, 0, s>>>(e->dqkv, 3 * d, (bf16*)xn, d, n, d);   // xn is free after the QKV product
+        rc = attn_tc_chunks_launch(e, xn, ao, e->self_k, e->self_v, c.max_tokens, c.max_tokens, l, cap->chunk_lens,
+                                   cap->chunk_slots, cap->tc_chunks, cap->t_pad, true, s);
+        if (rc < 0) return rc;
+        attn_done = rc == WDZ_OK;
+        e->launches += 1;
+      }
+    }
+#endif
+    if (!attn_done && (rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
     if ((rc = gemm(EPI_RESID, ao, d, w.out_w, w.out_b, e->dx, d, n, d, d, w.xq_w, wb))) return rc;
 
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s))) return rc;
@@ -539,7 +559,20 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
     }
     ap.q = e->dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
     ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
-    if ((rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
+    attn_done = false;
+#ifdef WDZ_WITH_TC
+    if constexpr (kBf16) {
+      if (cap && cap->tc_chunks > 0) {
+        cast_rows_kernel<<<n, 256, 0, s>>>(e->dq, d, (bf16*)xn, d, n, d);          // xn is free after the query product
+        rc = attn_tc_chunks_launch(e, xn, ao, e->cross_k, e->cross_v, c.n_audio_ctx, c.n_audio_ctx, l, cap->chunk_lens,
+                                   cap->chunk_slots, cap->tc_chunks, cap->t_pad, false, s);
+        if (rc < 0) return rc;
+        attn_done = rc == WDZ_OK;
+        e->launches += 1;
+      }
+    }
+#endif
+    if (!attn_done && (rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
     if ((rc = gemm(EPI_RESID, ao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d, w.fc1_w, 4 * wb))) return rc;
 
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, xn, d, n, d, s))) return rc;
@@ -633,8 +666,35 @@ static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int 
                     128, 3))
     return 1;
   atc::AttnTcParams p{};
-  p.out = (bf16*)out; p.T = T; p.d = d; p.n_kv = (T + atc::KT - 1) / atc::KT; p.status = e->status;
-  atc::attn_enc_tc_kernel<<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, p);
+  p.out = (bf16*)out; p.out_rows = T; p.d = d; p.Tq = T; p.Tk = T;
+  p.q_col0 = 0; p.k_col0 = d; p.v_col0 = 2 * d;
+  p.status = e->status;
+  atc::attn_enc_tc_kernel<<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, mq, mq, p);
+  e->launches += 1;
+  return WDZ_OK;
+}
+
+// Teacher-forced pass: the t_pad query rows of each chunk (bf16 [chunks * t_pad, d]) against the cache rows of
+// the chunk's slot in layer `layer`; cache [layers * slots, S, d].  Causal = self-attention over the chunk's own
+// rows, else all n_keys cross keys.
+static int attn_tc_chunks_launch(wdz_engine* e, const void* q, void* out, const void* cache_k, const void* cache_v,
+                                 int64_t S, int n_keys, int layer, const int* chunk_lens, const int* chunk_slots,
+                                 int n_chunks, int t_pad, bool causal, cudaStream_t s) {
+  const wdz_config& c = e->cfg;
+  const int d = c.n_text_state, H = c.n_text_head;
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)cache_k | (uintptr_t)cache_v) & 15 || d % 8) return 1;
+  CUtensorMap mq, mk, mv;
+  const uint64_t zs = (uint64_t)c.n_text_layer * c.n_slots;
+  if (!tc::make_map(&mq, q, (uint64_t)d, (uint64_t)t_pad, (uint64_t)n_chunks, (uint64_t)d * 2, (uint64_t)t_pad * d * 2, 128, 3) ||
+      !tc::make_map(&mk, cache_k, (uint64_t)d, (uint64_t)S, zs, (uint64_t)d * 2, (uint64_t)S * d * 2, 128, 3) ||
+      !tc::make_map(&mv, cache_v, (uint64_t)d, (uint64_t)S, zs, (uint64_t)d * 2, (uint64_t)S * d * 2, 128, 3))
+    return 1;
+  atc::AttnTcParams p{};
+  p.out = (bf16*)out; p.out_rows = t_pad; p.d = d; p.Tq = t_pad; p.Tk = n_keys;
+  p.lens = chunk_lens; p.kv_z = chunk_slots; p.kv_z_base = layer * c.n_slots; p.kv_z_limit = c.n_slots;
+  p.causal = causal ? 1 : 0;
+  p.status = e->status;
+  atc::attn_enc_tc_kernel<<<dim3((t_pad + atc::QT - 1) / atc::QT, H, n_chunks), 192, atc::SMEM_BYTES, s>>>(mq, mk, mv, p);
   e->launches += 1;
   return WDZ_OK;
 }
@@ -1470,11 +1530,22 @@ int wdz_align_matrix(wdz_engine* e, const int32_t* tokens_dev, const int32_t* ch
   float* rstd = mean + (int64_t)n_chunks * nh * Ta;
   // the pass overwrites the self-attention rows of the chunks' slots from position 0
   reset_seqlens_kernel<<<(n_chunks + 255) / 256, 256, 0, st>>>(chunk_slots_dev, e->seq_lens, n_chunks, c.n_slots);
-  for (int64_t r0 = 0; r0 < rows; r0 += c.max_rows) {
-    const int n = (int)(rows - r0 < c.max_rows ? rows - r0 : c.max_rows);
+  // bf16 with room for whole chunks in one forward call: attention of the pass on the tensor cores
+  bool tc_pass = false;
+#ifdef WDZ_WITH_TC
+  tc_pass = c.dtype == WDZ_BF16 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE) && t_pad <= c.max_rows;
+#endif
+  const int64_t group = tc_pass ? (int64_t)(c.max_rows / t_pad) * t_pad : c.max_rows;
+  for (int64_t r0 = 0; r0 < rows; r0 += group) {
+    const int n = (int)(rows - r0 < group ? rows - r0 : group);
     align_rows_kernel<<<(n + 255) / 256, 256, 0, st>>>(chunk_slots_dev, chunk_lens_dev, t_pad, (int)r0, n, c.n_slots, e->al_slots, e->al_pos);
     e->launches += 1;
-    AlignCapture cap{qcap, rows, r0};
+    AlignCapture cap{qcap, rows, r0, 0, t_pad, nullptr, nullptr};
+    if (tc_pass) {
+      cap.tc_chunks = n / t_pad;
+      cap.chunk_lens = chunk_lens_dev + r0 / t_pad;
+      cap.chunk_slots = chunk_slots_dev + r0 / t_pad;
+    }
     rc = c.dtype == WDZ_BF16
              ? forward_rows_impl<bf16>(e, tokens_dev + r0, e->al_slots, e->al_pos, n, nullptr, 0, st, &cap)
              : forward_rows_impl<float>(e, tokens_dev + r0, e->al_slots, e->al_pos, n, nullptr, 0, st, &cap);
@@ -1508,12 +1579,14 @@ int wdz_dtw(wdz_engine* e, const float* matrix_dev, int64_t chunk_stride, int64_
     return e->fail(WDZ_ECAPACITY, "wdz_dtw: %d x %d cells do not fit one CTA's shared memory (rows <= 511, rows x cols / 4 <= ~200 KB)",
                    max_rows, max_cols);
   if (col_lo_dev && limit_stride < max_rows) return e->fail(WDZ_EINVAL, "wdz_dtw: limit_stride %d < max_rows %d", limit_stride, max_rows);
+  if (ld < max_cols || (n_chunks > 1 && chunk_stride < ld)) return e->fail(WDZ_EINVAL, "wdz_dtw: ld %lld < max_cols %d or chunk stride too small", (long long)ld, max_cols);
   DtwParams p{};
   p.mat = matrix_dev; p.chunk_stride = chunk_stride; p.ld = ld;
   p.row0 = row0_dev; p.n_rows = n_rows_dev; p.n_cols = n_cols_dev;
   p.col_lo = col_lo_dev; p.col_hi = col_hi_dev; p.limit_stride = limit_stride;
   p.max_rows = max_rows; p.max_cols = max_cols; p.path_cap = max_rows + max_cols;
   p.text_idx = text_idx_out_dev; p.time_idx = time_idx_out_dev; p.path_len = path_len_out_dev;
+  p.status = e->status;
   dtw_kernel<<<n_chunks, 512, dtw_smem_bytes(max_rows, max_cols), (cudaStream_t)s>>>(p);
   e->launches += 1;
   WDZ_LAUNCH_CHECK(e, "dtw");

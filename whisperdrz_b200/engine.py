@@ -464,9 +464,13 @@ class Engine:
         ti = torch.empty(B, cap, dtype=torch.int32, device=self.device)
         tj = torch.empty(B, cap, dtype=torch.int32, device=self.device)
         ln = torch.empty(B, dtype=torch.int32, device=self.device)
+        row0_d, rows_d, cols_d = self._i32(row0), self._i32(n_rows), self._i32(n_cols)   # kept alive past the launch
+        if min(int(r) for r in row0) < 0 or max(int(r) + int(n) for r, n in zip(row0, n_rows)) > matrix.shape[1] \
+                or max_cols > matrix.shape[2]:
+            raise ValueError("dtw: a chunk's rows or columns lie outside the matrix")
         self._check(self.lib.wdz_dtw(
-            self.h, matrix.data_ptr(), matrix.stride(0), matrix.stride(1), self._i32(row0).data_ptr(),
-            self._i32(n_rows).data_ptr(), self._i32(n_cols).data_ptr(),
+            self.h, matrix.data_ptr(), matrix.stride(0), matrix.stride(1), row0_d.data_ptr(),
+            rows_d.data_ptr(), cols_d.data_ptr(),
             None if lo_d is None else lo_d.data_ptr(), None if hi_d is None else hi_d.data_ptr(), max_rows, B,
             max_rows, max_cols, ti.data_ptr(), tj.data_ptr(), ln.data_ptr(), self._stream()))
         ti_h, tj_h, ln_h = ti.cpu().numpy(), tj.cpu().numpy(), ln.cpu().numpy()
