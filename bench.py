@@ -130,7 +130,9 @@ def run_reference_arm(args):
 
 def workload_config(args) -> dict:
     return {"workload": f"batched 30 s chunks end to end (log-mel + {args.model} encoder + prefill + "
-                        f"{args.new_tokens}-token greedy decode with timestamp-pair rules), random-init weights",
+                        f"{args.new_tokens}-token greedy decode with timestamp-pair rules"
+                        + (" + DTW word timing of every window at token level" if getattr(args, "align", False) else "")
+                        + "), random-init weights",
             "chunks_per_gpu_per_step": args.clips, "new_tokens": args.new_tokens, "prompt_len": len(PROMPT),
             "parallelism": f"dp{args.gpus} (independent chunks, no collective on the path)",
             "l2": "working set per decode step (cross K/V of all slots) is far larger than the 126 MB L2"}
@@ -151,12 +153,16 @@ def main():
     ap.add_argument("--host-rules", action="store_true", help="rule state on the host, one decode step per round trip")
     ap.add_argument("--steps-per-poll", type=int, default=8)
     ap.add_argument("--engine-flags", type=int, default=0, help="WDZ_FLAG_* bits (A/B runs)")
+    ap.add_argument("--align", action="store_true",
+                    help="also run the DTW word-timing alignment on every finished window (token-level words); "
+                         "not part of the headline workload, named in config.workload when on")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
 
     import torch.distributed as dist
     from whisperdrz_b200 import synth
+    from whisperdrz_b200.alignment import token_aligner
     from whisperdrz_b200.dims import ModelDimensions
     from whisperdrz_b200.engine import Engine
     from whisperdrz_b200.rules import timestamp_tables
@@ -174,14 +180,15 @@ def main():
     dims = ModelDimensions.from_name(args.model)
     sd = init_state_dict(dims, 0)
     eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(16, args.clips),
-                 flags=args.engine_flags,
+                 flags=args.engine_flags, max_rows=max(args.clips, 64, 1792 if args.align else 0),
                  tables=timestamp_tables(dims.n_vocab))
     audio_host = torch.from_numpy(synth.clips([1000 * rank + i + 1 for i in range(args.clips)])).pin_memory()
     audio_dev = audio_host.to(dev)
 
     def one_step(src):
         tr = Transcriber(eng, max_new_tokens=args.new_tokens, max_continuations=0,
-                         device_rules=not args.host_rules, steps_per_poll=args.steps_per_poll)
+                         device_rules=not args.host_rules, steps_per_poll=args.steps_per_poll,
+                         aligner=token_aligner if args.align else None)
         for i in range(args.clips):
             tr.pending_chunks.append({"audio": src[i], "id": f"chunk_{i}", "duration": 30.0, "offset": 0.0})
         out = []

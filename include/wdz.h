@@ -269,8 +269,10 @@ int wdz_align_capacity(wdz_engine* e, int t_pad);
  * against the cached cross keys, softmax over the audio columns below audio_caps_dev[b], normalises each
  * (head, column) over the chunk's rows, median-filters (width 7, reflect) along audio and averages the
  * heads.  matrix_out_dev: f32 [n_chunks][t_pad][n_audio_ctx], rows past a chunk's length zero.
- * The pass writes the self-attention rows of the chunks' slots from position 0 (their decoded window is
- * finished) and resets those slots' lengths; slots of one call must be distinct. */
+ * bf16 engines with max_rows >= t_pad run the pass for whole chunks on the tensor cores and leave the self
+ * cache alone.  Otherwise the pass goes row by row through the decode kernels: it then writes the
+ * self-attention rows of the chunks' slots from position 0 (their decoded window is finished), resets those
+ * slots' lengths, and the slots of one call must be distinct. */
 int wdz_align_matrix(wdz_engine* e, const int32_t* tokens_dev, const int32_t* chunk_lens_dev,
                      const int32_t* chunk_slots_dev, const int32_t* audio_caps_dev, int n_chunks, int t_pad,
                      float* matrix_out_dev, wdz_stream s);

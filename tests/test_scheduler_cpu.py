@@ -243,3 +243,73 @@ def test_continuation_windows_restart_at_the_last_closing_timestamp():
     tr0 = Transcriber(eng0, max_new_tokens=12, max_continuations=0)
     _patch_rules_dev(tr0)
     assert tr0.transcribe(torch.randn(16000 * 30)).raw_chunks[0]["windows"] == 1
+
+
+class AlignStubEngine(StubEngine):
+    """Adds the alignment calls: the 'matrix' makes the cheapest path a straight diagonal, and the DTW is
+    the oracle's, so the scheduler's bookkeeping (which tokens are words, window offsets, what a continuation
+    keeps) is what gets tested."""
+    dims = type("D", (), {"n_audio_ctx": 1500})()
+
+    def __init__(self):
+        super().__init__()
+        self.align_calls = []
+        self.heads = None
+
+    def align_configure(self, heads):
+        self.heads = list(heads)
+
+    def align_matrix(self, tokens, lens, slots, caps):
+        self.align_calls.append((np.asarray(tokens).copy(), list(lens), list(slots), list(caps)))
+        B, T = np.asarray(tokens).shape
+        m = torch.zeros(B, T, 1500)
+        for b in range(B):
+            for t in range(lens[b]):
+                m[b, t, min(1499, 10 * t)] = 5.0          # high attention = low cost along a diagonal
+        return m
+
+    def dtw(self, matrix, row0, n_rows, n_cols, limits=None):
+        from oracle import oracle
+        out = []
+        for b in range(matrix.shape[0]):
+            x = -matrix[b, row0[b]: row0[b] + n_rows[b], : n_cols[b]].numpy()
+            if limits is not None:
+                lo, hi = limits[b]
+                cols = np.arange(x.shape[1])[None, :]
+                x = np.where((cols < lo[:, None]) | (cols >= hi[:, None]), np.inf, x)
+            out.append(oracle.dtw_path(x))
+        return out
+
+
+def test_finished_windows_are_aligned_before_their_slot_is_reused():
+    from whisperdrz_b200 import alignment
+    eng = AlignStubEngine()
+    tr = Transcriber(eng, max_new_tokens=40, max_continuations=0, aligner=alignment.token_aligner)
+    _patch_rules_dev(tr)
+    res = tr.transcribe(torch.randn(16000 * 70))              # three chunks over two prefill batches of the 4-slot stub
+    assert eng.heads == alignment.ALIGNMENT_HEADS_LARGE_V3 and tr.windows_aligned == len(res.raw_chunks) == 3
+    for r in res.raw_chunks:
+        words = r["word_times"]
+        text_pos = [i for i, t in enumerate(r["tokens"]) if t < TOK_EOT]
+        assert [w[0] for w in words] == text_pos               # every text token is a word, in order
+        starts = [w[1] for w in words]
+        assert starts == sorted(starts) and all(w[2] >= w[1] for w in words)
+        assert starts[0] >= r["offset"] and words[-1][2] <= r["offset"] + 30.0 + 1e-6
+    # the pass saw sot + lang + transcribe + no-timestamps + the text tokens + eot, in the chunk's own slot
+    toks, lens, slots, caps = eng.align_calls[0]
+    assert toks[0, :4].tolist() == [50258, 50259, 50360, 50364] and toks[0, lens[0] - 1] == TOK_EOT
+    assert all(0 <= s < eng.n_slots for s in slots) and caps[0] == 1500
+
+
+def test_continuation_keeps_the_words_of_the_kept_tokens():
+    from whisperdrz_b200 import alignment
+    eng = AlignStubEngine()
+    eng.emit_eot = False
+    tr = Transcriber(eng, max_new_tokens=12, max_continuations=2, aligner=alignment.token_aligner)
+    _patch_rules_dev(tr)
+    r = tr.transcribe(torch.randn(16000 * 30)).raw_chunks[0]
+    assert r["windows"] == 3 and tr.windows_aligned == 3
+    idx = [w[0] for w in r["word_times"]]
+    assert idx == sorted(idx) and len(set(idx)) == len(idx)
+    assert all(r["tokens"][i] < TOK_EOT for i in idx)            # indices point at text tokens of the stitched chunk
+    assert len(idx) >= 3 and all(w[2] >= w[1] >= 0.0 for w in r["word_times"])

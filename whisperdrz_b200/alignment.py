@@ -130,6 +130,38 @@ def word_times_from_path(text_idx: np.ndarray, time_idx: np.ndarray, word_lens: 
     return list(zip(jump_times[boundaries[:-1]].tolist(), jump_times[boundaries[1:]].tolist()))
 
 
+def token_aligner(tokens: list[int], ts_begin: int = 50365, ts_end: int = 51865, eot: int = TOK_EOT, max_tokens: int = 440) -> list[dict]:
+    """Chunk records for the generated tokens of one window when no tokenizer is at hand: every text token
+    is a word of one token (timestamp and special tokens are dropped), and a timestamp pair that encloses
+    exactly one text token anchors it, as the reference anchors a word the decoder timed itself.
+    A caller that holds the tokenizer passes its own function instead, re-tokenising the text at character
+    level as the reference does (``tokens_chars`` dtw_align.py:256-293).  Returns a list of dicts with
+    ids, word_lens, word_anchors, tag_anchors and token_pos (index of each word's token in ``tokens``),
+    split so that no chunk exceeds ``max_tokens`` ids."""
+    ids, pos, anchors = [], [], []
+    open_t, inside = None, []
+    for i, t in enumerate(tokens):
+        if ts_begin <= t <= ts_end:
+            sec = (t - ts_begin) * 0.02
+            if open_t is None:
+                open_t, inside = sec, []
+            else:
+                if len(inside) == 1:
+                    anchors.append((inside[0], open_t, sec))
+                open_t = None
+        elif t < eot:
+            if open_t is not None:
+                inside.append(len(ids))
+            ids.append(int(t))
+            pos.append(i)
+    out = []
+    for c0 in range(0, len(ids), max_tokens):
+        c1 = min(len(ids), c0 + max_tokens)
+        out.append({"ids": ids[c0:c1], "word_lens": [1] * (c1 - c0), "token_pos": pos[c0:c1], "tag_anchors": [],
+                    "word_anchors": [(w - c0, a, b) for w, a, b in anchors if c0 <= w < c1]})
+    return [c for c in out if c["ids"]]
+
+
 def align_chunks(engine, chunks: list[AlignChunk], sot_sequence=SOT_SEQUENCE, no_timestamps: int = TOK_NO_TIMESTAMPS,
                  eot: int = TOK_EOT, slack_frames: int = 7) -> list[list[tuple[float, float]]]:
     """Word times of every chunk.  Chunks of one call must sit in distinct slots (a second chunk of the

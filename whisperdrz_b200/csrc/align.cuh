@@ -40,8 +40,9 @@ __global__ void align_rows_kernel(const int* __restrict__ chunk_slots, const int
   positions[r] = t;
 }
 
-// q f32 [n, ldq] of layer `layer` -> qcap[j][row_base + r][64] for every selected head j of that layer.
-__global__ void align_capture_kernel(const float* __restrict__ q, int64_t ldq, int n, int layer, AlignHeads hs,
+// q [n, ldq] of layer `layer` -> qcap[j][row_base + r][64] (f32) for every selected head j of that layer.
+template <typename TQ>
+__global__ void align_capture_kernel(const TQ* __restrict__ q, int64_t ldq, int n, int layer, AlignHeads hs,
                                      float* __restrict__ qcap, int64_t rows_total, int64_t row_base) {
   const int r = blockIdx.x;
   const int e = threadIdx.x & 63, which = threadIdx.x >> 6;   // blockDim = 64 * heads of this layer (<= 1024)
@@ -49,7 +50,7 @@ __global__ void align_capture_kernel(const float* __restrict__ q, int64_t ldq, i
   for (int j = 0; j < hs.n; ++j) {
     if (hs.layer[j] != layer) continue;
     if (seen++ == which) {
-      qcap[((int64_t)j * rows_total + row_base + r) * ALIGN_HD + e] = q[(int64_t)r * ldq + hs.head[j] * ALIGN_HD + e];
+      qcap[((int64_t)j * rows_total + row_base + r) * ALIGN_HD + e] = to_f(q[(int64_t)r * ldq + hs.head[j] * ALIGN_HD + e]);
       return;
     }
   }

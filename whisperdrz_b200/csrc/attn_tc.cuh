@@ -125,7 +125,14 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (z < 0 || z >= p.kv_z_limit) return;
     kvz = p.kv_z_base + z;
   }
-  if (q0 >= q_valid) return;
+  if (q0 >= q_valid) {
+    // padding queries: their output rows are zeroed so that later products of the pass stay finite
+    // (a padded row's V would otherwise reach valid rows as 0 x NaN)
+    const int rows = min(QT, p.Tq - q0);
+    for (int i = threadIdx.x; i < rows * 8; i += blockDim.x)
+      reinterpret_cast<uint4*>(p.out + ((int64_t)b * p.out_rows + q0 + (i >> 3)) * p.d + h * 64)[i & 7] = make_uint4(0, 0, 0, 0);
+    return;
+  }
   const int k_valid = p.causal ? min(q_valid, p.Tk) : p.Tk;          // keys that exist
   const int k_end = p.causal ? min(k_valid, q0 + QT) : k_valid;      // keys this tile can see
   const int n_kv = (k_end + KT - 1) / KT;
@@ -294,6 +301,10 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_ld32(lane_addr + COL_O + c * 32, v);
+        if (q >= q_valid && q < p.Tq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) reinterpret_cast<uint4*>(dst + c * 32)[g] = make_uint4(0, 0, 0, 0);
+        }
         if (q < q_valid) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {

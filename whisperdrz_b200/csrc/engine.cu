@@ -36,7 +36,8 @@ struct wdz_engine;
 static int gemm_tc_init(wdz_engine* e);
 static int gemm_tc_launch(wdz_engine* e, int epi, const GemmParams& p, cudaStream_t s);
 static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& p, cudaStream_t s);
-static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int T, int d, int H, cudaStream_t s);
+static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int T, int d, int H, cudaStream_t s,
+                          const int* lens = nullptr, bool causal = false);
 static int attn_tc_chunks_launch(wdz_engine* e, const void* q, void* out, const void* cache_k, const void* cache_v,
                                  int64_t S, int n_keys, int layer, const int* chunk_lens, const int* chunk_slots,
                                  int n_chunks, int t_pad, bool causal, cudaStream_t s);
@@ -465,10 +466,6 @@ GemvMmaParams mma_params(const void* x, int64_t ldx, const void* W, const void* 
 
 struct AlignCapture {   // teacher-forced alignment pass: keep the alignment heads' cross queries, stop after the last
   float* qcap; int64_t rows_total, row_base;
-  // tc_chunks > 0: the rows are tc_chunks whole chunks of t_pad tokens each, and attention runs on the tensor
-  // cores with a chunk's keys read once per 128 queries instead of once per query
-  int tc_chunks, t_pad;
-  const int* chunk_lens; const int* chunk_slots;
 };
 
 // tokens/slots/positions: device int32 [n].  Logits of the emit rows land in e->logits.
@@ -529,20 +526,7 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
     ap.layer = l;
     ap.q = e->dqkv; ap.ldq = 3 * d; ap.cache_k = e->self_k; ap.cache_v = e->self_v; ap.S = c.max_tokens;
     ap.positions = positions; ap.fixed_len = 0;
-    bool attn_done = false;
-#ifdef WDZ_WITH_TC
-    if constexpr (kBf16) {
-      if (cap && cap->tc_chunks > 0) {
-        cast_rows_kernel<<<n, 256, 0, s>>>(e->dqkv, 3 * d, (bf16*)xn, d, n, d);   // xn is free after the QKV product
-        rc = attn_tc_chunks_launch(e, xn, ao, e->self_k, e->self_v, c.max_tokens, c.max_tokens, l, cap->chunk_lens,
-                                   cap->chunk_slots, cap->tc_chunks, cap->t_pad, true, s);
-        if (rc < 0) return rc;
-        attn_done = rc == WDZ_OK;
-        e->launches += 1;
-      }
-    }
-#endif
-    if (!attn_done && (rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
+    if ((rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
     if ((rc = gemm(EPI_RESID, ao, d, w.out_w, w.out_b, e->dx, d, n, d, d, w.xq_w, wb))) return rc;
 
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s))) return rc;
@@ -551,7 +535,7 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
       int here = 0;
       for (int j = 0; j < e->al_heads.n; ++j) here += e->al_heads.layer[j] == l;
       if (here > 0) {
-        align_capture_kernel<<<n, 64 * here, 0, s>>>(e->dq, d, n, l, e->al_heads, cap->qcap, cap->rows_total, cap->row_base);
+        align_capture_kernel<float><<<n, 64 * here, 0, s>>>(e->dq, d, n, l, e->al_heads, cap->qcap, cap->rows_total, cap->row_base);
         e->launches += 1;
         WDZ_LAUNCH_CHECK(e, "align_capture");
       }
@@ -559,20 +543,7 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
     }
     ap.q = e->dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
     ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
-    attn_done = false;
-#ifdef WDZ_WITH_TC
-    if constexpr (kBf16) {
-      if (cap && cap->tc_chunks > 0) {
-        cast_rows_kernel<<<n, 256, 0, s>>>(e->dq, d, (bf16*)xn, d, n, d);          // xn is free after the query product
-        rc = attn_tc_chunks_launch(e, xn, ao, e->cross_k, e->cross_v, c.n_audio_ctx, c.n_audio_ctx, l, cap->chunk_lens,
-                                   cap->chunk_slots, cap->tc_chunks, cap->t_pad, false, s);
-        if (rc < 0) return rc;
-        attn_done = rc == WDZ_OK;
-        e->launches += 1;
-      }
-    }
-#endif
-    if (!attn_done && (rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
+    if ((rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
     if ((rc = gemm(EPI_RESID, ao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d, w.fc1_w, 4 * wb))) return rc;
 
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, xn, d, n, d, s))) return rc;
@@ -659,7 +630,8 @@ static int gemm_tc_init(wdz_engine* e) {
   return WDZ_OK;
 }
 
-static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int T, int d, int H, cudaStream_t s) {
+static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int T, int d, int H, cudaStream_t s,
+                          const int* lens, bool causal) {
   if (((uintptr_t)qkv | (uintptr_t)out) & 15 || d % 8) return 1;
   CUtensorMap mq;
   if (!tc::make_map(&mq, qkv, (uint64_t)3 * d, (uint64_t)T, (uint64_t)B, (uint64_t)3 * d * 2, (uint64_t)T * 3 * d * 2,
@@ -668,6 +640,7 @@ static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int 
   atc::AttnTcParams p{};
   p.out = (bf16*)out; p.out_rows = T; p.d = d; p.Tq = T; p.Tk = T;
   p.q_col0 = 0; p.k_col0 = d; p.v_col0 = 2 * d;
+  p.lens = lens; p.causal = causal ? 1 : 0;
   p.status = e->status;
   atc::attn_enc_tc_kernel<<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, mq, mq, p);
   e->launches += 1;
@@ -1464,6 +1437,58 @@ int wdz_rules_argmax(wdz_engine* e, const float* logits_dev, const wdz_rule_desc
 }
 
 // ---- word-timing alignment -------------------------------------------------
+}  // extern "C"
+
+#ifdef WDZ_WITH_TC
+// Teacher-forced pass over whole chunks (bf16): n = n_chunks * t_pad rows, chunk-major.  The rows of a chunk only
+// attend to each other (causally) and to the chunk's cross cache, so nothing is appended to the self cache:
+// Q, K and V of a layer are the columns of one bf16 [n, 3d] product, exactly the encoder's layout, and every
+// product runs on the 128 x 256 tcgen05 GEMM with its weights read once for all rows.
+static int align_pass_tc(wdz_engine* e, const int* tokens, int n, int n_chunks, int t_pad, const int* chunk_lens,
+                         const int* chunk_slots, const AlignCapture& cap, cudaStream_t s) {
+  const wdz_config& c = e->cfg;
+  const int d = c.n_text_state, H = c.n_text_head;
+  int rc;
+  bf16* xn = (bf16*)e->dxn;
+  bf16* ao = (bf16*)e->dao;
+  bf16* hid = (bf16*)e->dh;
+  bf16* qkvb = (bf16*)e->dqkv;
+  bf16* qb = (bf16*)e->dq;
+  embed_kernel<bf16><<<n, 256, 0, s>>>(tokens, e->al_pos, (const bf16*)e->tok_emb, (const bf16*)e->dec_pos, e->dx, n, d, c.n_vocab,
+                                       c.n_text_ctx);
+  e->launches += 1;
+  WDZ_LAUNCH_CHECK(e, "embed");
+  for (int l = 0; l <= e->al_last_layer && l < c.n_text_layer; ++l) {
+    const LayerW& w = e->dec[l];
+    if ((rc = launch_ln<bf16, bf16>(e, e->dx, d, nullptr, w.ln1_w, w.ln1_b, xn, d, n, d, s))) return rc;
+    if ((rc = enc_gemm<bf16>(e, EPI_STORE, dense_params(xn, d, w.qkv_w, w.qkv_b, qkvb, 3 * d, n, 3 * d, d), s))) return rc;
+    if ((rc = attn_tc_launch(e, qkvb, ao, n_chunks, t_pad, d, H, s, chunk_lens, true))) return rc < 0 ? rc : e->fail(WDZ_EINVAL, "alignment: attention shape");
+    if ((rc = enc_gemm<bf16>(e, EPI_RESID, dense_params(ao, d, w.out_w, w.out_b, e->dx, d, n, d, d), s))) return rc;
+
+    if ((rc = launch_ln<bf16, bf16>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s))) return rc;
+    if ((rc = enc_gemm<bf16>(e, EPI_STORE, dense_params(xn, d, w.xq_w, w.xq_b, qb, d, n, d, d), s))) return rc;
+    int here = 0;
+    for (int j = 0; j < e->al_heads.n; ++j) here += e->al_heads.layer[j] == l;
+    if (here > 0) {
+      align_capture_kernel<bf16><<<n, 64 * here, 0, s>>>(qb, d, n, l, e->al_heads, cap.qcap, cap.rows_total, cap.row_base);
+      e->launches += 1;
+      WDZ_LAUNCH_CHECK(e, "align_capture");
+    }
+    if (l >= e->al_last_layer) break;
+    if ((rc = attn_tc_chunks_launch(e, qb, ao, e->cross_k, e->cross_v, c.n_audio_ctx, c.n_audio_ctx, l, chunk_lens,
+                                    chunk_slots, n_chunks, t_pad, false, s)))
+      return rc < 0 ? rc : e->fail(WDZ_EINVAL, "alignment: attention shape");
+    if ((rc = enc_gemm<bf16>(e, EPI_RESID, dense_params(ao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d), s))) return rc;
+
+    if ((rc = launch_ln<bf16, bf16>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, xn, d, n, d, s))) return rc;
+    if ((rc = enc_gemm<bf16>(e, EPI_GELU, dense_params(xn, d, w.fc1_w, w.fc1_b, hid, 4 * d, n, 4 * d, d), s))) return rc;
+    if ((rc = enc_gemm<bf16>(e, EPI_RESID, dense_params(hid, 4 * d, w.fc2_w, w.fc2_b, e->dx, d, n, d, 4 * d), s))) return rc;
+  }
+  return WDZ_OK;
+}
+#endif
+
+extern "C" {
 int wdz_align_configure(wdz_engine* e, const int32_t* layer_head_pairs, int n_heads) {
   if (!e) return WDZ_EINVAL;
   if (!layer_head_pairs || n_heads < 1 || n_heads > ALIGN_MAX_HEADS)
@@ -1528,24 +1553,26 @@ int wdz_align_matrix(wdz_engine* e, const int32_t* tokens_dev, const int32_t* ch
   float* qcap = (float*)e->qkv;
   float* mean = qcap + (int64_t)nh * rows * ALIGN_HD;
   float* rstd = mean + (int64_t)n_chunks * nh * Ta;
-  // the pass overwrites the self-attention rows of the chunks' slots from position 0
-  reset_seqlens_kernel<<<(n_chunks + 255) / 256, 256, 0, st>>>(chunk_slots_dev, e->seq_lens, n_chunks, c.n_slots);
   // bf16 with room for whole chunks in one forward call: attention of the pass on the tensor cores
   bool tc_pass = false;
 #ifdef WDZ_WITH_TC
-  tc_pass = c.dtype == WDZ_BF16 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE) && t_pad <= c.max_rows;
+  tc_pass = c.dtype == WDZ_BF16 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE) && t_pad <= c.max_rows && c.n_text_state % 256 == 0;
 #endif
+  // the row-wise pass appends to the self-attention rows of the chunks' slots from position 0
+  if (!tc_pass) reset_seqlens_kernel<<<(n_chunks + 255) / 256, 256, 0, st>>>(chunk_slots_dev, e->seq_lens, n_chunks, c.n_slots);
   const int64_t group = tc_pass ? (int64_t)(c.max_rows / t_pad) * t_pad : c.max_rows;
   for (int64_t r0 = 0; r0 < rows; r0 += group) {
     const int n = (int)(rows - r0 < group ? rows - r0 : group);
     align_rows_kernel<<<(n + 255) / 256, 256, 0, st>>>(chunk_slots_dev, chunk_lens_dev, t_pad, (int)r0, n, c.n_slots, e->al_slots, e->al_pos);
     e->launches += 1;
-    AlignCapture cap{qcap, rows, r0, 0, t_pad, nullptr, nullptr};
+    AlignCapture cap{qcap, rows, r0};
+#ifdef WDZ_WITH_TC
     if (tc_pass) {
-      cap.tc_chunks = n / t_pad;
-      cap.chunk_lens = chunk_lens_dev + r0 / t_pad;
-      cap.chunk_slots = chunk_slots_dev + r0 / t_pad;
+      rc = align_pass_tc(e, tokens_dev + r0, n, n / t_pad, t_pad, chunk_lens_dev + r0 / t_pad, chunk_slots_dev + r0 / t_pad, cap, st);
+      if (rc) return rc;
+      continue;
     }
+#endif
     rc = c.dtype == WDZ_BF16
              ? forward_rows_impl<bf16>(e, tokens_dev + r0, e->al_slots, e->al_pos, n, nullptr, 0, st, &cap)
              : forward_rows_impl<float>(e, tokens_dev + r0, e->al_slots, e->al_pos, n, nullptr, 0, st, &cap);

@@ -13,8 +13,10 @@ What changes is the device side of each step: one rule-descriptor upload, one
 fused engine call (forward over all active rows, logit rules, argmax) and one
 4-byte-per-row download replace the reference's ~30 mask kernels, bucketed
 graph replay and six small copies.  Rules are the token-level subset of
-``whisperdrz_b200.rules``; text-level rules, DTW word timing and the text
-clean-up chain of the reference are not part of this path.
+``whisperdrz_b200.rules``; text-level rules and the text clean-up chain of the
+reference are not part of this path.  Word timing by DTW on the alignment
+heads (``_batch_align_slots`` :1419-1530) runs on every finished window when
+an ``aligner`` is given (``whisperdrz_b200.alignment``).
 """
 from __future__ import annotations
 
@@ -25,6 +27,7 @@ import torch
 
 from .dims import SAMPLE_RATE, TOK_EOT, TOK_LANG_EN, TOK_SOT, TOK_TRANSCRIBE
 from .rules import BatchRuleState, segments as token_segments
+from . import alignment
 
 
 @dataclass
@@ -46,6 +49,8 @@ class Slot:
     continuations: int = 0
     kept_tokens: list = field(default_factory=list)     # tokens of earlier windows of this chunk
     kept_segments: list = field(default_factory=list)
+    kept_words: list = field(default_factory=list)      # (token index in the chunk, start s, end s) of earlier windows
+    window_words: list = field(default_factory=list)    # (token index in the window, start s, end s), chunk-relative times
 
 
 def rules_to_array(rules: list[dict]) -> np.ndarray:
@@ -73,7 +78,8 @@ class Transcriber:
     def __init__(self, engine, BS: int | None = None, max_audio_length: float = 30.0,
                  max_new_tokens: int = 224, lang: str | None = "en", use_rules: bool = True,
                  text_decoder=None, max_continuations: int = 20, device_rules: bool | None = None,
-                 steps_per_poll: int = 8, min_refill: int = 1, max_refill_wait: int = 4):
+                 steps_per_poll: int = 8, min_refill: int = 1, max_refill_wait: int = 4,
+                 aligner=None, align_heads=None):
         """engine: ``whisperdrz_b200.engine.Engine`` (or an object with the same
         methods).  BS: concurrent slots, at most the engine's.  max_new_tokens:
         generated tokens per 30 s window before EOT is forced.  text_decoder:
@@ -87,7 +93,10 @@ class Transcriber:
         when at least this many can be prefilled together (the encoder is far
         more efficient on a batch of windows), or after ``max_refill_wait``
         scheduler iterations; the reference refills one by one
-        (transcriber.py:1790-1815, ``min_refill_batch = 1``), which is the default."""
+        (transcriber.py:1790-1815, ``min_refill_batch = 1``), which is the default.
+        aligner: ``tokens -> [chunk dict]`` (see ``alignment.token_aligner``); when given, every finished
+        window is aligned by DTW before its slot is released and results carry ``word_times``
+        (the reference's ``dtw_align=True``).  align_heads: (layer, head) pairs, default the large-v3 set."""
         self.engine = engine
         self.BS = BS or engine.n_slots
         if self.BS > engine.n_slots:
@@ -112,6 +121,10 @@ class Transcriber:
         self.steps = 0
         self.launch_rows = 0
         self._pin_audio = None
+        self.aligner = aligner
+        self.windows_aligned = 0
+        if aligner is not None:
+            engine.align_configure(align_heads or alignment.ALIGNMENT_HEADS_LARGE_V3)
 
     # ------------------------------------------------------------------ public
     def transcribe(self, audio) -> TranscribeResults:
@@ -161,6 +174,7 @@ class Transcriber:
         slot.stop_reason = ""
         slot.win_offset, slot.continuations = 0.0, 0
         slot.kept_tokens, slot.kept_segments = [], []
+        slot.kept_words, slot.window_words = [], []
 
     def _prefill_slots(self, slots: list[Slot]) -> None:
         """Log-mel + encoder + cross K/V + prompt for new slots, then their first token."""
@@ -248,6 +262,7 @@ class Transcriber:
                     if closes == 2 * len(segs):
                         n_keep = i + 1
                         break
+            slot.kept_words += [(len(slot.kept_tokens) + i, a, b) for i, a, b in slot.window_words if i < n_keep]
             slot.kept_tokens += toks[:n_keep]
             slot.kept_segments += segs
             slot.win_offset += max(last_end, 1.0)
@@ -259,12 +274,38 @@ class Transcriber:
         res = {k: v for k, v in c.items() if k not in ("audio", "mel")}
         res.update(id=c["id"], tokens=all_toks, stop_reason=slot.stop_reason, windows=slot.continuations + 1,
                    segments=slot.kept_segments + segs)
+        if self.aligner is not None:
+            res["word_times"] = slot.kept_words + [(len(slot.kept_tokens) + i, a, b) for i, a, b in slot.window_words]
         if self.text_decoder:
             res["prediction"] = self.text_decoder(all_toks)
         self.seconds_processed += duration
         slot.status, slot.chunk = "ready", None
         slot.kept_tokens, slot.kept_segments = [], []
+        slot.kept_words, slot.window_words = [], []
         return res
+
+    def _align_finished(self, slots: list[Slot]) -> None:
+        """DTW word timing of the windows that just finished, all in one batch, while their slots still hold
+        the windows' cross keys (transcriber.py:1419-1530 runs the same step before a slot is re-used)."""
+        chunks, owners = [], []
+        for s in slots:
+            raw = self._tok_cache[s.index] if self.device_rules else self.rule_state.slot_tokens(s.index)
+            toks = [t for t in raw if t != TOK_EOT]
+            s.window_words = []
+            c = s.chunk
+            left = max(0.0, c.get("duration", self.max_audio_length) - s.win_offset)
+            frames = int(min(self.max_audio_length, left) * alignment.FRAMES_PER_SECOND)
+            for rec in self.aligner(toks):
+                chunks.append(alignment.AlignChunk(slot=s.index, ids=rec["ids"], word_lens=rec["word_lens"], num_frames=frames,
+                                                   word_anchors=rec.get("word_anchors", []), tag_anchors=rec.get("tag_anchors", [])))
+                owners.append((s, rec["token_pos"]))
+        if not chunks:
+            return
+        times = alignment.align_chunks(self.engine, chunks)
+        self.windows_aligned += len(slots)
+        for (s, pos), wt in zip(owners, times):
+            base = s.chunk.get("offset", 0.0) + s.win_offset
+            s.window_words += [(p, round(a + base, 2), round(b + base, 2)) for p, (a, b) in zip(pos, wt)]
 
     @torch.inference_mode()
     def step(self) -> list[dict]:
@@ -315,6 +356,10 @@ class Transcriber:
             self.steps += 1
             self.launch_rows += len(active)
             self._accept(active, nxt.tolist())
+        if self.aligner is not None:
+            fin = [s for s in self.states if s.status == "finished"]
+            if fin:
+                self._align_finished(fin)
         for s in self.states:
             if s.status == "finished":
                 r = self._finish(s)
