@@ -180,7 +180,7 @@ def main():
     dims = ModelDimensions.from_name(args.model)
     sd = init_state_dict(dims, 0)
     eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(16, args.clips),
-                 flags=args.engine_flags, max_rows=max(args.clips, 64, 1792 if args.align else 0),
+                 flags=args.engine_flags, max_rows=max(args.clips, 64, 4096 if args.align else 0),
                  tables=timestamp_tables(dims.n_vocab))
     audio_host = torch.from_numpy(synth.clips([1000 * rank + i + 1 for i in range(args.clips)])).pin_memory()
     audio_dev = audio_host.to(dev)

@@ -43,6 +43,7 @@ struct AttnTcParams {
   int kv_z_base, kv_z_limit;   // added to kv_z[b] (layer * slots); slots
   int q_col0, k_col0, v_col0;  // first column of head 0 in the Q / K / V maps
   int causal;           // key k visible to query q only if k <= q
+  int one_map;          // Q, K and V are columns of one tensor: only the first tensor map is fetched
   DevStatus* status;
 };
 
@@ -146,8 +147,10 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmQ) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmK) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmV) : "memory");
+    if (!p.one_map) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmK) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmV) : "memory");
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
@@ -161,6 +164,8 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
+      const CUtensorMap* mk = p.one_map ? &tmQ : &tmK;
+      const CUtensorMap* mv = p.one_map ? &tmQ : &tmV;
       tma_load_3d(q_s, &tmQ, q_full, p.q_col0 + h * 64, q0, b);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j % KV_STAGES;
@@ -168,8 +173,8 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!mbar_wait(kv_empty + st, phase ^ 1, abort_flag, p.status)) break;
         uint8_t* k_dst = kv_s + st * 2 * TILE_BYTES;
         mbar_expect_tx(kv_full + st, 2 * TILE_BYTES);
-        tma_load_3d(k_dst, &tmK, kv_full + st, p.k_col0 + h * 64, j * KT, kvz);
-        tma_load_3d(k_dst + TILE_BYTES, &tmV, kv_full + st, p.v_col0 + h * 64, j * KT, kvz);
+        tma_load_3d(k_dst, mk, kv_full + st, p.k_col0 + h * 64, j * KT, kvz);
+        tma_load_3d(k_dst + TILE_BYTES, mv, kv_full + st, p.v_col0 + h * 64, j * KT, kvz);
       }
     }
   } else if (warp == 1) {

@@ -640,7 +640,7 @@ static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int 
   atc::AttnTcParams p{};
   p.out = (bf16*)out; p.out_rows = T; p.d = d; p.Tq = T; p.Tk = T;
   p.q_col0 = 0; p.k_col0 = d; p.v_col0 = 2 * d;
-  p.lens = lens; p.causal = causal ? 1 : 0;
+  p.lens = lens; p.causal = causal ? 1 : 0; p.one_map = 1;
   p.status = e->status;
   atc::attn_enc_tc_kernel<<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, mq, mq, p);
   e->launches += 1;
