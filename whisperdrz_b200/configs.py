@@ -1,7 +1,7 @@
 """Timings of the named workloads other than the batched end-to-end case that
 bench.py times, on one GPU:
 
-    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5]
+    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5 align align_small]
 
 cfg1  one 30 s clip, 4-token prompt, 224 greedy tokens with EOS suppressed (latency; fp32 and bf16)
 cfg2  encoder only, bf16, 16 clips: log-mel + conv stem + 32 layers (time, TFLOP/s)
@@ -9,6 +9,9 @@ cfg3  batched decode, bf16: 32 slots over precomputed cross K/V, prompts U{4..64
       forced EOS at the drawn length, timestamp-pair rules (tokens/s)
 cfg5  serving: requests with log-uniform durations 5 s - 10 min and Poisson arrivals, chunks of different
       requests packed into shared decode steps (throughput, p50/p99 time to final transcript)
+align word-timing alignment of 8 finished windows, 445 tokens each (the longest a chunk gets), bf16: the
+      teacher-forced pass + scores + cost matrix, and the DTW with its download (``align_small``: 155 tokens,
+      the size a 224-token window gives at token level)
 
 Inputs are the seeded synthetic stand-ins of ``synth``; weights are seeded random init.  Prints one JSON
 object per workload."""
@@ -167,12 +170,38 @@ def cfg5(dims, sd, n_req=96, slots=256, seed=4, min_refill=1):
             "decode_steps": tr.steps, "mean_rows_per_step": tr.launch_rows / max(tr.steps, 1)}
 
 
+def align(dims, sd, n_chunks=8, n_ids=440, reps=3):
+    from . import alignment as A
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=n_chunks, max_clips=8, max_rows=4096)
+    g = torch.Generator(device="cpu").manual_seed(6)
+    xa = (torch.randn(n_chunks, dims.n_audio_ctx, dims.n_audio_state, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    slots = list(range(n_chunks))
+    e.cross_kv(xa, slots)
+    e.align_configure(A.ALIGNMENT_HEADS_LARGE_V3)
+    rng = np.random.RandomState(0)
+    tokens, lens = A.build_full_tokens([rng.randint(0, 50000, size=n_ids).tolist() for _ in range(n_chunks)])
+    caps = [dims.n_audio_ctx] * n_chunks
+    ms_matrix, m = _timed(lambda: e.align_matrix(tokens, lens, slots, caps), reps=reps)
+    ms_dtw, paths = _timed(lambda: e.dtw(m, [3] * n_chunks, [ln - 4 for ln in lens], caps), reps=reps)
+    e.device_status()
+    rows = n_chunks * tokens.shape[1]
+    n_layers = max(l for l, _ in A.ALIGNMENT_HEADS_LARGE_V3) + 1
+    d = dims.n_text_state
+    gflop = rows * n_layers * 2.0 * (12 * d * d) / 1e9            # the pass's products (attention not counted)
+    out = {"workload": f"align: {n_chunks} windows x {tokens.shape[1]} tokens, bf16, alignment heads of large-v3",
+           "matrix_ms": ms_matrix, "dtw_ms": ms_dtw, "ms_per_window": (ms_matrix + ms_dtw) / n_chunks,
+           "pass_gemm_tflops": gflop / ms_matrix, "path_len": int(len(paths[0][0]))}
+    e.close()
+    return out
+
+
 def main(argv):
     want = argv or ["cfg1", "cfg2", "cfg3", "cfg5"]
     dims = ModelDimensions.from_name("large-v3")
     sd = init_state_dict(dims, 0)
     fns = {"cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg5": cfg5,
-           "cfg5b": lambda d, s: cfg5(d, s, min_refill=8)}
+           "cfg5b": lambda d, s: cfg5(d, s, min_refill=8), "align": align,
+           "align_small": lambda d, s: align(d, s, n_ids=150)}
     with torch.inference_mode():
         for w in want:
             print(json.dumps(fns[w](dims, sd)), flush=True)

@@ -250,28 +250,41 @@ __global__ void __launch_bounds__(512) dtw_kernel(DtwParams p) {
       hi = min(p.col_hi[(int64_t)b * p.limit_stride + i - 1], M);
     }
   }
-  auto xval = [&](int j) -> float {   // j = 1..M
-    const int c = j - 1;
-    return (c >= lo && c < hi) ? -mrow[c] : INFINITY;
+  // The row's costs come through a ring of three float4 (columns c .. c + 11): a thread reads its row left to
+  // right, one cell per diagonal, and with all rows live the lines do not stay in L1, so each load is issued
+  // eight or more diagonals before its first use.
+  const bool vec_ok = (p.ld & 3) == 0 && (p.chunk_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(p.mat) & 15) == 0;
+  auto load4 = [&](int c0) -> float4 {
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (mrow == nullptr || c0 >= M) return v;
+    if (vec_ok && c0 + 3 < p.ld) return *reinterpret_cast<const float4*>(mrow + c0);
+    v.x = mrow[c0];
+    if (c0 + 1 < M) v.y = mrow[c0 + 1];
+    if (c0 + 2 < M) v.z = mrow[c0 + 2];
+    if (c0 + 3 < M) v.w = mrow[c0 + 3];
+    return v;
   };
+  float4 r0 = load4(0), r1 = load4(4), r2 = load4(8);
   // diagonal k holds cost[i][k - i]; buffers rotate: d0 = k-2, d1 = k-1, d2 = k
   float* d0 = diag; float* d1 = diag + dstride; float* d2 = diag + 2 * dstride;
   // diagonal 1: cost[0][1] and cost[1][0] are borders (inf), already in place
-  float xnext = (i >= 1 && i <= N) ? xval(1) : 0.0f;                     // the row's first cell is on diagonal i + 1
   __syncthreads();
   for (int k = 2; k <= N + M; ++k) {
     if (i <= N) {
       const int j = k - i;
       float v = INFINITY;                                                // borders: row 0 (k > 0), column 0
       if (i >= 1 && j >= 1 && j <= M) {
+        const int c = j - 1;
+        const float raw = (c & 3) == 0 ? r0.x : (c & 3) == 1 ? r0.y : (c & 3) == 2 ? r0.z : r0.w;
+        const float x = (c >= lo && c < hi) ? -raw : INFINITY;
         const float c0 = d0[i - 1], c1 = d1[i - 1], c2 = d1[i];
-        int tdir; float c;
-        if (c0 <= c1 && c0 <= c2) { c = c0; tdir = 0; }
-        else if (c1 <= c2) { c = c1; tdir = 1; }
-        else { c = c2; tdir = 2; }
-        v = xnext + c;
-        trace[(i - 1) * rowbytes + ((j - 1) >> 2)] |= (uint8_t)(tdir << (((j - 1) & 3) * 2));
-        if (j < M) xnext = xval(j + 1);
+        int tdir; float cmin;
+        if (c0 <= c1 && c0 <= c2) { cmin = c0; tdir = 0; }
+        else if (c1 <= c2) { cmin = c1; tdir = 1; }
+        else { cmin = c2; tdir = 2; }
+        v = x + cmin;
+        trace[(i - 1) * rowbytes + (c >> 2)] |= (uint8_t)(tdir << ((c & 3) * 2));
+        if ((c & 3) == 3) { r0 = r1; r1 = r2; r2 = load4(c + 9); }
       }
       if (i >= 1 ? (j >= 0 && j <= M) : true) d2[i] = v;
     }

@@ -98,6 +98,9 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
 
+// kGeneral = false is the encoder's instantiation: no lengths, no slot indirection, no causal rule, one tensor
+// map; those branches are then compiled out of its inner loops.
+template <bool kGeneral>
 __global__ void __launch_bounds__(192, 2)
 attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
@@ -119,9 +122,11 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * QT, h = blockIdx.y, b = blockIdx.z;
   // uniform over the CTA: nothing to do for tiles past the batch entry's queries or for skipped entries
-  const int q_valid = p.lens ? min(p.lens[b], p.Tq) : p.Tq;
+  const int q_valid = (kGeneral && p.lens) ? min(p.lens[b], p.Tq) : p.Tq;
+  const bool causal = kGeneral && p.causal;
+  const bool one_map = !kGeneral || p.one_map;
   int kvz = b;
-  if (p.kv_z) {
+  if (kGeneral && p.kv_z) {
     const int z = p.kv_z[b];
     if (z < 0 || z >= p.kv_z_limit) return;
     kvz = p.kv_z_base + z;
@@ -134,8 +139,8 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       reinterpret_cast<uint4*>(p.out + ((int64_t)b * p.out_rows + q0 + (i >> 3)) * p.d + h * 64)[i & 7] = make_uint4(0, 0, 0, 0);
     return;
   }
-  const int k_valid = p.causal ? min(q_valid, p.Tk) : p.Tk;          // keys that exist
-  const int k_end = p.causal ? min(k_valid, q0 + QT) : k_valid;      // keys this tile can see
+  const int k_valid = causal ? min(q_valid, p.Tk) : p.Tk;            // keys that exist
+  const int k_end = causal ? min(k_valid, q0 + QT) : k_valid;        // keys this tile can see
   const int n_kv = (k_end + KT - 1) / KT;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -147,7 +152,7 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmQ) : "memory");
-    if (!p.one_map) {
+    if (!one_map) {
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmK) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmV) : "memory");
     }
@@ -164,8 +169,8 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
-      const CUtensorMap* mk = p.one_map ? &tmQ : &tmK;
-      const CUtensorMap* mv = p.one_map ? &tmQ : &tmV;
+      const CUtensorMap* mk = one_map ? &tmQ : &tmK;
+      const CUtensorMap* mv = one_map ? &tmQ : &tmV;
       tma_load_3d(q_s, &tmQ, q_full, p.q_col0 + h * 64, q0, b);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j % KV_STAGES;
@@ -217,8 +222,8 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       const int k0 = j * KT;
       // only the last key tile has columns past the sequence; under the causal rule also the diagonal tile
-      const bool tail = k0 + KT > k_valid || (p.causal && k0 + KT > q0);
-      const int k_lim = p.causal ? min(k_valid, q + 1) : k_valid;   // keys [0, k_lim) are visible to this row
+      const bool tail = k0 + KT > k_valid || (causal && k0 + KT > q0);
+      const int k_lim = causal ? min(k_valid, q + 1) : k_valid;   // keys [0, k_lim) are visible to this row
       float mx = -INFINITY;
 #pragma unroll 1
       for (int hf = 0; hf < 2; ++hf) {
@@ -306,7 +311,7 @@ attn_enc_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_ld32(lane_addr + COL_O + c * 32, v);
-        if (q >= q_valid && q < p.Tq) {
+        if (kGeneral && q >= q_valid && q < p.Tq) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) reinterpret_cast<uint4*>(dst + c * 32)[g] = make_uint4(0, 0, 0, 0);
         }

@@ -617,8 +617,10 @@ static int gemm_tc_init(wdz_engine* e) {
     cudaError_t ce = cudaGetLastError();
     return e->fail(WDZ_ECUDA, "gemm_tc smem attribute: %s", cudaGetErrorString(ce));
   }
-  if (cudaFuncSetAttribute(atc::attn_enc_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::SMEM_BYTES) !=
-      cudaSuccess) {
+  if (cudaFuncSetAttribute(atc::attn_enc_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::SMEM_BYTES) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(atc::attn_enc_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::SMEM_BYTES) !=
+          cudaSuccess) {
     cudaError_t ce = cudaGetLastError();
     return e->fail(WDZ_ECUDA, "attn_enc_tc smem attribute: %s", cudaGetErrorString(ce));
   }
@@ -642,7 +644,10 @@ static int attn_tc_launch(wdz_engine* e, const void* qkv, void* out, int B, int 
   p.q_col0 = 0; p.k_col0 = d; p.v_col0 = 2 * d;
   p.lens = lens; p.causal = causal ? 1 : 0; p.one_map = 1;
   p.status = e->status;
-  atc::attn_enc_tc_kernel<<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, mq, mq, p);
+  if (lens || causal)
+    atc::attn_enc_tc_kernel<true><<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, mq, mq, p);
+  else
+    atc::attn_enc_tc_kernel<false><<<dim3((T + atc::QT - 1) / atc::QT, H, B), 192, atc::SMEM_BYTES, s>>>(mq, mq, mq, p);
   e->launches += 1;
   return WDZ_OK;
 }
@@ -667,7 +672,7 @@ static int attn_tc_chunks_launch(wdz_engine* e, const void* q, void* out, const 
   p.lens = chunk_lens; p.kv_z = chunk_slots; p.kv_z_base = layer * c.n_slots; p.kv_z_limit = c.n_slots;
   p.causal = causal ? 1 : 0;
   p.status = e->status;
-  atc::attn_enc_tc_kernel<<<dim3((t_pad + atc::QT - 1) / atc::QT, H, n_chunks), 192, atc::SMEM_BYTES, s>>>(mq, mk, mv, p);
+  atc::attn_enc_tc_kernel<true><<<dim3((t_pad + atc::QT - 1) / atc::QT, H, n_chunks), 192, atc::SMEM_BYTES, s>>>(mq, mk, mv, p);
   e->launches += 1;
   return WDZ_OK;
 }
