@@ -16,7 +16,9 @@ Stored in align.npz: the inputs (clip seeds, char-level ids per chunk, heads,
 audio caps, anchors), slices and sums of the raw scores, slices of the cost
 matrices, the full negated and band-masked matrices the DTW ran on (a few
 hundred KB), the paths and word times; and for seeded random matrices of
-several shapes (up to 444 x 1500, some with blocked bands) the paths only.
+several shapes (up to 444 x 1500, some with blocked bands) the paths only;
+and for 40 random sets of word / tag anchors the columns ``_apply_anchor_bands``
+leaves open in every row.
 """
 from __future__ import annotations
 
@@ -123,6 +125,40 @@ def main():
         out[f"path_time{bi}"] = time_idx.astype(np.int16)
         out[f"word_times{bi}"] = np.array([[s, e] for _, s, e in times], dtype=np.float64)
         print(f"chunk {bi}: {neg.shape} path {len(text_idx)} blocked {int(np.isinf(neg).sum())} words {len(times)}")
+    # anchor bands alone: random word / tag anchors (unordered, overlapping, out of range, one-sided tags)
+    # through _apply_anchor_bands on a zero matrix; stored as the allowed column range of every row
+    arng = np.random.RandomState(17)
+    n_band_cases = 40
+    for ci in range(n_band_cases):
+        n_words = int(arng.randint(1, 12))
+        wl = [int(v) for v in arng.randint(1, 6, size=n_words)]
+        n_rows = 1 + sum(wl) - int(arng.randint(0, 2))          # sometimes one row short of the last word
+        cap_b = int(arng.choice([200, 730, 1500]))
+        words = [f"w{i}" for i in range(n_words)] + [""]
+        word_tokens = [[0] * n for n in wl] + [[tok.eot]]
+        wa = []
+        for _ in range(int(arng.randint(0, 5))):
+            st = float(arng.uniform(-1.0, cap_b / 50.0 + 1.0))
+            wa.append((int(arng.randint(0, n_words + 2)), round(st, 2), round(st + float(arng.uniform(-0.2, 3.0)), 2)))
+        ta = []
+        for _ in range(int(arng.randint(0, 3))):
+            st = float(arng.uniform(-1.0, cap_b / 50.0 + 1.0))
+            pl = None if arng.rand() < 0.3 else int(arng.randint(0, n_words + 1))
+            nl = None if arng.rand() < 0.3 else int(arng.randint(0, n_words + 1))
+            ta.append((round(st, 2), round(st + float(arng.uniform(0.0, 2.0)), 2), pl, nl))
+        z = np.zeros((n_rows, cap_b), dtype=np.float32)
+        D._apply_anchor_bands(z, words, word_tokens, cap_b, wa, ta, slack_frames=7)
+        ok = ~np.isinf(z)
+        lo = np.array([int(np.argmax(r)) if r.any() else 0 for r in ok], dtype=np.int32)
+        hi = np.array([cap_b - int(np.argmax(r[::-1])) if r.any() else 0 for r in ok], dtype=np.int32)
+        assert all(ok[i, lo[i]:hi[i]].all() and ok[i].sum() == hi[i] - lo[i] for i in range(n_rows))   # contiguous
+        out[f"band{ci}_shape"] = np.array([n_rows, cap_b])
+        out[f"band{ci}_word_lens"] = np.array(wl)
+        out[f"band{ci}_word_anchors"] = np.array(wa, dtype=np.float64).reshape(-1, 3)
+        out[f"band{ci}_tag_anchors"] = np.array([[a, b, -1 if c is None else c, -1 if d is None else d] for a, b, c, d in ta],
+                                                dtype=np.float64).reshape(-1, 4)
+        out[f"band{ci}_lo"], out[f"band{ci}_hi"] = lo, hi
+    out["n_band_cases"] = np.int64(n_band_cases)
     out["random_cases"] = np.array(RANDOM_CASES)
     for ci, (N, M, banded) in enumerate(RANDOM_CASES):
         ti, tj = D._dtw_numba(random_case(100 + ci, N, M, banded))

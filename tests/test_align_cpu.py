@@ -95,6 +95,25 @@ def test_anchor_limits_and_word_times_match_reference(gold):
     assert A.word_times_from_path(np.array([0, 0, 1]), np.array([0, 1, 2]), [3, 3]) == []   # path too short
 
 
+def test_anchor_limits_on_random_anchor_sets_match_reference(gold):
+    """40 random sets of word and tag anchors (unordered, overlapping, past the last word or the audio,
+    one-sided tags) through the reference's _apply_anchor_bands: the same cells stay allowed."""
+    n_blocked_rows = 0
+    for ci in range(int(gold["n_band_cases"])):
+        n_rows, cap = (int(v) for v in gold[f"band{ci}_shape"])
+        wa = [(int(a), b, c) for a, b, c in gold[f"band{ci}_word_anchors"].tolist()]
+        ta = [(a, b, None if c < 0 else int(c), None if d < 0 else int(d)) for a, b, c, d in gold[f"band{ci}_tag_anchors"].tolist()]
+        lo, hi = A.anchor_row_limits(n_rows, cap, gold[f"band{ci}_word_lens"].tolist(), wa, ta)
+        rlo, rhi = gold[f"band{ci}_lo"], gold[f"band{ci}_hi"]
+        for i in range(n_rows):
+            if rhi[i] <= rlo[i]:
+                assert hi[i] <= lo[i], (ci, i)
+                n_blocked_rows += 1
+            else:
+                assert (lo[i], hi[i]) == (rlo[i], rhi[i]), (ci, i, lo[i], hi[i], rlo[i], rhi[i])
+    assert n_blocked_rows >= 0
+
+
 def test_alignment_heads_constant_matches_the_reference_mask():
     import base64
     import gzip

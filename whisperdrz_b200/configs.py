@@ -1,7 +1,7 @@
 """Timings of the named workloads other than the batched end-to-end case that
 bench.py times, on one GPU:
 
-    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5 align align_small]
+    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5 align align_small products]
 
 cfg1  one 30 s clip, 4-token prompt, 224 greedy tokens with EOS suppressed (latency; fp32 and bf16)
 cfg2  encoder only, bf16, 16 clips: log-mel + conv stem + 32 layers (time, TFLOP/s)
@@ -12,6 +12,8 @@ cfg5  serving: requests with log-uniform durations 5 s - 10 min and Poisson arri
 align word-timing alignment of 8 finished windows, 445 tokens each (the longest a chunk gets), bf16: the
       teacher-forced pass + scores + cost matrix, and the DTW with its download (``align_small``: 155 tokens,
       the size a 224-token window gives at token level)
+products  the decode step's weight products (wdz_linear_rows) at 32 and 256 token rows, each shape replayed
+      inside a CUDA graph over a 300 MB rotation of weights (so they stream from HBM as in a decode step)
 
 Inputs are the seeded synthetic stand-ins of ``synth``; weights are seeded random init.  Prints one JSON
 object per workload."""
@@ -195,13 +197,43 @@ def align(dims, sd, n_chunks=8, n_ids=440, reps=3):
     return out
 
 
+def products(dims, sd, row_counts=(32, 256)):
+    small = ModelDimensions.from_name("test-small")
+    e = Engine(small, init_state_dict(small, 0), dtype=torch.bfloat16, n_slots=2, max_clips=1)
+    d = dims.n_text_state
+    shapes = {"qkv": (3 * d, d), "attn_out / cross_out (residual)": (d, d), "cross_q": (d, d), "fc1": (4 * d, d),
+              "fc2 (residual)": (d, 4 * d)}
+    g = torch.Generator(device="cpu").manual_seed(8)
+    out = {"workload": "decode products in a CUDA graph, weights rotated through 300 MB", "us": {}}
+    for name, (N, K) in shapes.items():
+        nw = max(2, int(300e6 / (N * K * 2)))
+        ws = [(torch.randn(N, K, generator=g) * 0.03).to(torch.bfloat16).cuda() for _ in range(nw)]
+        for M in row_counts:
+            x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+            acc = torch.zeros(M, N, device="cuda") if "residual" in name else None
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                e.linear_rows(x, ws[0], out=acc)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(nw):
+                    e.linear_rows(x, ws[i], out=acc)
+            ms, _ = _timed(graph.replay, reps=5, warm=2)
+            out["us"][f"{name} N{N} K{K} rows{M}"] = round(ms * 1e3 / nw, 2)
+        del ws
+    e.close()
+    return out
+
+
 def main(argv):
     want = argv or ["cfg1", "cfg2", "cfg3", "cfg5"]
     dims = ModelDimensions.from_name("large-v3")
     sd = init_state_dict(dims, 0)
     fns = {"cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg5": cfg5,
            "cfg5b": lambda d, s: cfg5(d, s, min_refill=8), "align": align,
-           "align_small": lambda d, s: align(d, s, n_ids=150)}
+           "align_small": lambda d, s: align(d, s, n_ids=150), "products": products}
     with torch.inference_mode():
         for w in want:
             print(json.dumps(fns[w](dims, sd)), flush=True)
