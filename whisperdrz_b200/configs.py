@@ -1,7 +1,7 @@
 """Timings of the named workloads other than the batched end-to-end case that
 bench.py times, on one GPU:
 
-    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5 align align_small products]
+    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5 align align_small products products_once]
 
 cfg1  one 30 s clip, 4-token prompt, 224 greedy tokens with EOS suppressed (latency; fp32 and bf16)
 cfg2  encoder only, bf16, 16 clips: log-mel + conv stem + 32 layers (time, TFLOP/s)
@@ -197,7 +197,8 @@ def align(dims, sd, n_chunks=8, n_ids=440, reps=3):
     return out
 
 
-def products(dims, sd, row_counts=(32, 256)):
+def products(dims, sd, row_counts=(32, 256), once=False):
+    """``once``: every shape launched a single time outside a graph, on cold weights (for profiler captures)."""
     small = ModelDimensions.from_name("test-small")
     e = Engine(small, init_state_dict(small, 0), dtype=torch.bfloat16, n_slots=2, max_clips=1)
     d = dims.n_text_state
@@ -211,6 +212,10 @@ def products(dims, sd, row_counts=(32, 256)):
         for M in row_counts:
             x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
             acc = torch.zeros(M, N, device="cuda") if "residual" in name else None
+            if once:
+                ms, _ = _timed(lambda: e.linear_rows(x, ws[1], out=acc), reps=1, warm=0)
+                out["us"][f"{name} N{N} K{K} rows{M}"] = round(ms * 1e3, 2)
+                continue
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -233,7 +238,8 @@ def main(argv):
     sd = init_state_dict(dims, 0)
     fns = {"cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg5": cfg5,
            "cfg5b": lambda d, s: cfg5(d, s, min_refill=8), "align": align,
-           "align_small": lambda d, s: align(d, s, n_ids=150), "products": products}
+           "align_small": lambda d, s: align(d, s, n_ids=150), "products": products,
+           "products_once": lambda d, s: products(d, s, row_counts=(256,), once=True)}
     with torch.inference_mode():
         for w in want:
             print(json.dumps(fns[w](dims, sd)), flush=True)

@@ -79,11 +79,12 @@ __device__ __forceinline__ float dot64(const float* __restrict__ q, const bf16* 
 
 // One warp per text row: lane a handles columns a, a + 32, ...; the row's scores stay in registers
 // (ceil(Ta / 32) <= ALIGN_COLS_PER_LANE), softmax over columns < cap, zeros from cap on.
-// grid = (ceil(t_pad / 8), heads, chunks), block = 256.
+// grid = (ceil(t_pad / 8), heads, chunks), block = 256.  The lens / slots / caps pointers and w start at the
+// first chunk of this launch; qcap is indexed with the chunk's number in the whole pass (chunk0 + b).
 constexpr int ALIGN_COLS_PER_LANE = 48;   // Ta <= 1536
 template <typename T>
 __global__ void __launch_bounds__(256)
-align_scores_kernel(const float* __restrict__ qcap, int64_t rows_total, int t_pad, const int* __restrict__ chunk_lens,
+align_scores_kernel(const float* __restrict__ qcap, int64_t rows_total, int chunk0, int t_pad, const int* __restrict__ chunk_lens,
                     const int* __restrict__ chunk_slots, const int* __restrict__ caps, AlignHeads hs,
                     const T* __restrict__ cross_k, int n_slots, int Ta, int d, float* __restrict__ w) {
   __shared__ float qs[8][ALIGN_HD];
@@ -93,7 +94,7 @@ align_scores_kernel(const float* __restrict__ qcap, int64_t rows_total, int t_pa
   const bool live = t < chunk_lens[b] && t < t_pad && slot >= 0 && slot < n_slots;   // uniform over the warp
   if (live && lane < 16)
     *reinterpret_cast<float4*>(&qs[warp][lane * 4]) =
-        *reinterpret_cast<const float4*>(qcap + ((int64_t)j * rows_total + (int64_t)b * t_pad + t) * ALIGN_HD + lane * 4);
+        *reinterpret_cast<const float4*>(qcap + ((int64_t)j * rows_total + (int64_t)(chunk0 + b) * t_pad + t) * ALIGN_HD + lane * 4);
   __syncwarp();
   if (!live) return;
   const int cap = min(max(caps[b], 0), Ta);

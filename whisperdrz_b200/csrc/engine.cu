@@ -106,6 +106,7 @@ struct wdz_engine {
   int* ts_log = nullptr;                             // [n_slots, max_tokens] generated tokens per slot
   TsParams ts_params{50257, 50365, 51865, 50, 100, 1u, 2u};
   int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
+  int sw_bm64 = 0;            // 64-feature tiles for the complete-sum decode products (tuning experiments)
   int row_tile_override = 0;  // > 0: row tile of the decode products (32..256; tuning experiments)
   int ksplit_override = 0;  // > 0: fixed K split of the residual decode products (tuning experiments)
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
@@ -690,7 +691,10 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   //  - residual sums (K split, red.global.add): a single row tile when K is long (operand bytes dominate),
   //    else 64- or 128-row tiles, and as many K splits as fill the wave.
   const int mpad_all = (g.M + 31) / 32 * 32;
-  const int tiles = (g.N + tc::BM - 1) / tc::BM;
+  // complete-sum products have one weight stream per feature tile: 64-feature tiles double the streams
+  const int bm = (epi != EPI_RESID && e->sw_bm64) ? 64 : tc::BM;
+  p.bm = bm;
+  const int tiles = (g.N + bm - 1) / bm;
   p.kblocks = g.K / tc::BK;
   int row_tile = mpad_all;
   if (e->row_tile_override > 0) {
@@ -715,20 +719,20 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   p.kb_per_split = (p.kblocks + ksplit - 1) / ksplit;
   ksplit = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
   p.epi = epi == EPI_QKV_CACHE ? tc::EPI_SW_QKV_CACHE : epi;
-  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mpad >> 3) << 17) | ((uint32_t)(tc::BM >> 4) << 24);
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mpad >> 3) << 17) | ((uint32_t)(bm >> 4) << 24);
   p.cache_k = g.cache_k; p.cache_v = g.cache_v; p.slots = g.slots; p.positions = g.positions;
   p.layer = g.layer; p.n_slots = g.n_slots; p.S = g.S; p.d = g.d;
   // (no L2 prefetch of the next weights here: measured slower at 32-256 rows, it competes with this
   // kernel's own latency-bound TMA stream; the small-row kernel keeps it)
   p.status = e->status;
   CUtensorMap mw, mx;
-  if (!tc::make_map(&mw, g.W, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * g.N, tc::BM, 2))
+  if (!tc::make_map(&mw, g.W, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * g.N, (uint32_t)bm, 2))
     return 1;
   if (!tc::make_map(&mx, g.x, (uint64_t)g.K, (uint64_t)g.M, 1, (uint64_t)g.ldx * 2, (uint64_t)g.ldx * 2 * g.M,
                     (uint32_t)p.mpad, 2))
     return 1;
   launch_pdl(e, tc::gemm_tc_swap_kernel, dim3(tiles, ksplit, row_tiles), dim3(tc::THREADS),
-             (size_t)tc::sw_smem_bytes(row_tile), s, mw, mx, p);
+             (size_t)tc::sw_smem_bytes(row_tile, bm), s, mw, mx, p);
   WDZ_LAUNCH_CHECK(e, "gemm_tc_swap");
   return WDZ_OK;
 }
@@ -785,6 +789,7 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
   e->esz = c.dtype == WDZ_BF16 ? 2 : 4;
   if (const char* ks = getenv("WDZ_KSPLIT")) e->ksplit_override = atoi(ks);
   if (const char* rt = getenv("WDZ_ROWTILE")) e->row_tile_override = atoi(rt) / 32 * 32;
+  if (const char* b64 = getenv("WDZ_SW_BM64")) e->sw_bm64 = atoi(b64);
   if (const char* gm = getenv("WDZ_GEMV_MAX_ROWS")) e->gemv_max_rows = atoi(gm);
   e->enc.resize(c.n_audio_layer);
   e->dec.resize(c.n_text_layer);
@@ -1515,17 +1520,20 @@ int wdz_align_configure(wdz_engine* e, const int32_t* layer_head_pairs, int n_he
   return WDZ_OK;
 }
 
-// Scratch of the alignment lives in encoder activations that are idle between encoder calls: the scores
-// [chunks, heads, t_pad, Ta] f32 in the MLP hidden buffer, queries and column statistics in the QKV buffer.
+// Scratch of the alignment lives in encoder activations that are idle between encoder calls: queries and column
+// statistics in the QKV buffer (this bounds the chunks of one call), the scores [chunks, heads, t_pad, Ta] f32 in
+// the MLP hidden buffer, filled and consumed a few chunks at a time.
+static int64_t align_score_chunks(const wdz_engine* e, int t_pad) {   // chunks whose scores fit at once
+  const wdz_config& c = e->cfg;
+  const int64_t hid_bytes = (int64_t)e->esz * c.max_clips * c.n_audio_ctx * 4 * c.n_audio_state;
+  return hid_bytes / ((int64_t)e->al_heads.n * t_pad * c.n_audio_ctx * 4);
+}
 static int64_t align_capacity(const wdz_engine* e, int t_pad) {
   const wdz_config& c = e->cfg;
-  if (e->al_heads.n < 1 || t_pad < 1) return 0;
-  const int64_t hid_bytes = (int64_t)e->esz * c.max_clips * c.n_audio_ctx * 4 * c.n_audio_state;
+  if (e->al_heads.n < 1 || t_pad < 1 || align_score_chunks(e, t_pad) < 1) return 0;
   const int64_t qkv_bytes = (int64_t)e->esz * c.max_clips * c.n_audio_ctx * 3 * c.n_audio_state;
-  const int64_t per_w = (int64_t)e->al_heads.n * t_pad * c.n_audio_ctx * 4;
   const int64_t per_q = (int64_t)e->al_heads.n * t_pad * ALIGN_HD * 4 + (int64_t)e->al_heads.n * c.n_audio_ctx * 8 + 512;
-  const int64_t a = hid_bytes / per_w, b = qkv_bytes / per_q;
-  return a < b ? a : b;
+  return qkv_bytes / per_q;
 }
 
 int wdz_align_capacity(wdz_engine* e, int t_pad) {
@@ -1583,16 +1591,22 @@ int wdz_align_matrix(wdz_engine* e, const int32_t* tokens_dev, const int32_t* ch
              : forward_rows_impl<float>(e, tokens_dev + r0, e->al_slots, e->al_pos, n, nullptr, 0, st, &cap);
     if (rc) return rc;
   }
-  const dim3 gs((t_pad + 7) / 8, nh, n_chunks);
-  if (c.dtype == WDZ_BF16)
-    align_scores_kernel<bf16><<<gs, 256, 0, st>>>(qcap, rows, t_pad, chunk_lens_dev, chunk_slots_dev, audio_caps_dev, e->al_heads,
-                                                  (const bf16*)e->cross_k, c.n_slots, Ta, c.n_text_state, w);
-  else
-    align_scores_kernel<float><<<gs, 256, 0, st>>>(qcap, rows, t_pad, chunk_lens_dev, chunk_slots_dev, audio_caps_dev, e->al_heads,
-                                                   (const float*)e->cross_k, c.n_slots, Ta, c.n_text_state, w);
-  align_colstats_kernel<<<dim3((Ta + 127) / 128, nh, n_chunks), 128, 0, st>>>(w, nh, t_pad, Ta, chunk_lens_dev, mean, rstd);
-  align_matrix_kernel<<<dim3(t_pad, n_chunks), 256, 0, st>>>(w, mean, rstd, nh, t_pad, Ta, chunk_lens_dev, matrix_out_dev);
-  e->launches += 4;
+  const int per = (int)std::min<int64_t>(align_score_chunks(e, t_pad), n_chunks);
+  for (int c0 = 0; c0 < n_chunks; c0 += per) {
+    const int nb = std::min(per, n_chunks - c0);
+    const dim3 gs((t_pad + 7) / 8, nh, nb);
+    const int* lens_b = chunk_lens_dev + c0;
+    if (c.dtype == WDZ_BF16)
+      align_scores_kernel<bf16><<<gs, 256, 0, st>>>(qcap, rows, c0, t_pad, lens_b, chunk_slots_dev + c0, audio_caps_dev + c0,
+                                                    e->al_heads, (const bf16*)e->cross_k, c.n_slots, Ta, c.n_text_state, w);
+    else
+      align_scores_kernel<float><<<gs, 256, 0, st>>>(qcap, rows, c0, t_pad, lens_b, chunk_slots_dev + c0, audio_caps_dev + c0,
+                                                     e->al_heads, (const float*)e->cross_k, c.n_slots, Ta, c.n_text_state, w);
+    align_colstats_kernel<<<dim3((Ta + 127) / 128, nh, nb), 128, 0, st>>>(w, nh, t_pad, Ta, lens_b, mean, rstd);
+    align_matrix_kernel<<<dim3(t_pad, nb), 256, 0, st>>>(w, mean, rstd, nh, t_pad, Ta, lens_b,
+                                                         matrix_out_dev + (int64_t)c0 * t_pad * Ta);
+    e->launches += 3;
+  }
   WDZ_LAUNCH_CHECK(e, "align_matrix");
   return WDZ_OK;
 }
