@@ -56,12 +56,14 @@ __global__ void align_capture_kernel(const TQ* __restrict__ q, int64_t ldq, int 
   }
 }
 
+// q sits in shared memory (one row per warp) and is read 16 bytes at a time.
 __device__ __forceinline__ float dot64(const float* __restrict__ q, const float* __restrict__ k) {
   float s = 0.0f;
 #pragma unroll
   for (int e = 0; e < ALIGN_HD; e += 4) {
     const float4 kv = *reinterpret_cast<const float4*>(k + e);
-    s += q[e] * kv.x + q[e + 1] * kv.y + q[e + 2] * kv.z + q[e + 3] * kv.w;
+    const float4 qv = *reinterpret_cast<const float4*>(q + e);
+    s += qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
   }
   return s;
 }
@@ -71,8 +73,8 @@ __device__ __forceinline__ float dot64(const float* __restrict__ q, const bf16* 
   for (int e = 0; e < ALIGN_HD; e += 8) {
     float kv[8];
     load_vec(k + e, kv);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s += q[e + i] * kv[i];
+    const float4 qa = *reinterpret_cast<const float4*>(q + e), qb = *reinterpret_cast<const float4*>(q + e + 4);
+    s += qa.x * kv[0] + qa.y * kv[1] + qa.z * kv[2] + qa.w * kv[3] + qb.x * kv[4] + qb.y * kv[5] + qb.z * kv[6] + qb.w * kv[7];
   }
   return s;
 }
@@ -87,7 +89,7 @@ __global__ void __launch_bounds__(256)
 align_scores_kernel(const float* __restrict__ qcap, int64_t rows_total, int chunk0, int t_pad, const int* __restrict__ chunk_lens,
                     const int* __restrict__ chunk_slots, const int* __restrict__ caps, AlignHeads hs,
                     const T* __restrict__ cross_k, int n_slots, int Ta, int d, float* __restrict__ w) {
-  __shared__ float qs[8][ALIGN_HD];
+  __shared__ __align__(16) float qs[8][ALIGN_HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + warp, j = blockIdx.y, b = blockIdx.z;
   const int slot = chunk_slots[b];
