@@ -2,7 +2,7 @@
 
 Run where the reference is mounted:
 
-    PYTHONPATH=<reference>/src python tests/golden/make_align_golden.py
+    PYTHONPATH=<reference>/src python tests/golden/make_align_golden.py [--large]
 
 The unmodified reference runs on the CPU: ``CrossAttnCapture`` around
 ``model.decoder(full_tokens, xa)`` and ``compute_attention`` give the raw QK^T
@@ -64,7 +64,64 @@ def random_case(seed: int, N: int, M: int, banded: int) -> np.ndarray:
     return x
 
 
+def large():
+    """Full-size case (``--large``): large-v3 dimensions, seeded weights, one 30 s clip, a 44-id chunk with two word
+    anchors, the reference's own ten alignment heads.  Stores slices of the cost matrix, the DTW path of the
+    band-masked matrix and the word times (align_large.npz, ~100 KB).  Needs ~14 GB of RAM and a few minutes."""
+    dims = ModelDimensions.from_name("large-v3")
+    m = WhisperDRZ(RefDims(**dims.as_dict()), config=Config()).float().eval()
+    m.load_state_dict(init_state_dict(dims, 0), strict=False)
+    tok = m.tokenizer
+    tomel = LogMelSpectrogram(dims.n_mels)
+    audio = synth.clips([1])
+    mel = torch.stack([tomel(torch.from_numpy(a).unsqueeze(0), target_frames=3000)[0] for a in audio])
+    with torch.inference_mode():
+        xa = m.encoder(mel)
+    word_lens = [5, 3, 6, 2, 7, 4, 4, 6, 3, 4]
+    rng = np.random.RandomState(9)
+    ids = [int(t) for t in rng.randint(0, 50000, size=sum(word_lens))]
+    full_tokens, actual_lens = D._build_full_tokens_batch(tok, [ids], xa.device)
+    head_mask = D.make_head_mask(m)
+    heads = [tuple(r) for r in head_mask.nonzero().tolist()]
+    with D.CrossAttnCapture(m, layers={l for l, _ in heads}) as cap:
+        with torch.inference_mode():
+            m.decoder(full_tokens, xa)
+        weights = cap.compute_attention(head_mask)
+    if weights.dim() == 3:
+        weights = weights.unsqueeze(0)
+    caps = [1380]
+    orig_pin, orig_sync = D._pinned_host_buffer, torch.cuda.synchronize
+    D._pinned_host_buffer = lambda shape, dtype: torch.empty(shape, dtype=dtype)
+    torch.cuda.synchronize = lambda *a, **k: None
+    try:
+        matrices = D._dtw_prep_batch(weights, actual_lens, caps).copy()
+    finally:
+        D._pinned_host_buffer, torch.cuda.synchronize = orig_pin, orig_sync
+    sot_len = len(tok.sot_sequence)
+    words = [f"w{i}" for i in range(len(word_lens))] + [""]
+    word_tokens, o = [], 0
+    for n in word_lens:
+        word_tokens.append(ids[o:o + n])
+        o += n
+    word_tokens.append([tok.eot])
+    word_anchors = [(2, 6.4, 7.9), (7, 19.0, 20.5)]
+    neg = np.ascontiguousarray(-matrices[0, sot_len: actual_lens[0] - 1, :caps[0]], dtype=np.float32)
+    D._apply_anchor_bands(neg, words, word_tokens, caps[0], word_anchors, [], slack_frames=7)
+    text_idx, time_idx = D._dtw_numba(neg)
+    times = D._dtw_from_neg_matrix(neg, words, word_tokens)
+    np.savez_compressed(
+        os.path.join(HERE, "align_large.npz"), clip_seed=np.int64(1), heads=np.array(heads), ids=np.array(ids),
+        word_lens=np.array(word_lens), audio_cap=np.int64(caps[0]), actual_len=np.int64(actual_lens[0]),
+        word_anchors=np.array(word_anchors, dtype=np.float64), matrix_slice=matrices[0][:, ::7],
+        xa_slice=xa[0, ::50].numpy(), path_text=text_idx.astype(np.int16), path_time=time_idx.astype(np.int16),
+        word_times=np.array([[s, e] for _, s, e in times], dtype=np.float64))
+    print("wrote align_large.npz", os.path.getsize(os.path.join(HERE, "align_large.npz")) // 1024, "KB; path", len(text_idx),
+          "word times", [round(float(s), 2) for _, s, _ in times])
+
+
 def main():
+    if "--large" in sys.argv:
+        return large()
     dims = ModelDimensions.from_name("test-small")
     m = WhisperDRZ(RefDims(**dims.as_dict()), config=Config()).float().eval()
     m.load_state_dict(init_state_dict(dims, 0), strict=False)

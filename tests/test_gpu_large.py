@@ -72,3 +72,43 @@ def test_large_v3_bf16_within_tolerance(large, golden):
     assert rel < 1e-2, rel
     assert worst < 3e-2, worst
     e.close()
+
+
+@pytest.mark.parametrize("dtype,tol_max,tol_mean,frames", [(torch.float32, 5e-3, 5e-4, 1), (torch.bfloat16, 0.6, 0.03, 25)])
+def test_large_v3_word_timing_alignment(large, golden_dir, dtype, tol_max, tol_mean, frames):
+    """Word-timing alignment at full size against the reference's recording (tests/golden/make_align_golden.py
+    --large: its ten alignment heads, a 44-id chunk with two word anchors on a 30 s clip).  fp32: cost matrix
+    (z-scores of order one) within 5e-3 and the word times within one 20 ms frame; bf16 (tcgen05 pass): matrix
+    within 0.6 max / 0.03 mean and word times within 0.5 s (the path may slip between near-equal costs), the
+    anchored words inside their bands in both."""
+    from whisperdrz_b200 import alignment as A
+    from whisperdrz_b200.engine import Engine
+    g = np.load(os.path.join(golden_dir, "align_large.npz"))
+    dims, sd = large
+    assert [tuple(int(v) for v in h) for h in g["heads"]] == A.ALIGNMENT_HEADS_LARGE_V3
+    e = Engine(dims, sd, dtype=dtype, n_slots=2, max_clips=1, max_rows=64)
+    audio = synth.clips([int(g["clip_seed"])])
+    xa = e.encode(e.logmel(torch.from_numpy(audio).cuda()))
+    gx = torch.from_numpy(g["xa_slice"])
+    assert float((xa[0, ::50].float().cpu() - gx).norm() / gx.norm()) < (1e-4 if dtype == torch.float32 else 1e-2)
+    e.cross_kv(xa, [1])
+    e.align_configure(A.ALIGNMENT_HEADS_LARGE_V3)
+    ids, word_lens = g["ids"].tolist(), g["word_lens"].tolist()
+    tokens, lens = A.build_full_tokens([ids])
+    assert lens[0] == int(g["actual_len"])
+    cap = int(g["audio_cap"])
+    m = e.align_matrix(tokens, lens, [1], [cap]).cpu()
+    e.device_status()
+    ref = torch.from_numpy(g["matrix_slice"])
+    diff = (m[0, : lens[0], :cap][:, ::7] - ref[: lens[0]]).abs()
+    assert float(diff.max()) < tol_max and float(diff.mean()) < tol_mean, (float(diff.max()), float(diff.mean()))
+    anchors = [(int(a), b, c) for a, b, c in g["word_anchors"].tolist()]
+    chunk = A.AlignChunk(slot=1, ids=ids, word_lens=word_lens, num_frames=2 * cap, word_anchors=anchors)
+    times = np.array(A.align_chunks(e, [chunk])[0])
+    e.device_status()
+    want = g["word_times"]
+    assert times.shape == want.shape
+    assert np.abs(times - want).max() <= 0.02 * frames + 1e-9, (times.tolist(), want.tolist())
+    for wi, a_s, a_e in anchors:                       # anchored words stay inside their bands (7 frames of slack)
+        assert times[wi, 0] >= a_s - 0.15 and times[wi, 0] <= a_e + 0.15
+    e.close()
