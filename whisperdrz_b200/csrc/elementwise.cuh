@@ -86,7 +86,8 @@ template <typename TP, typename TO>
 __global__ void __launch_bounds__(128)
 layernorm_row_kernel(const float* __restrict__ x, int64_t ldx, const int* __restrict__ row_idx,
                      const TP* __restrict__ gamma, const TP* __restrict__ beta,
-                     TO* __restrict__ y, int64_t ldy, int rows, int d) {
+                     TO* __restrict__ y, int64_t ldy, int rows, int d,
+                     float* __restrict__ zero = nullptr, int64_t ldz = 0, int nz = 0) {
   pdl_trigger();
   constexpr int MAXI = 4;  // float4 per thread: d <= 2048
   __shared__ float red[2][4];
@@ -100,6 +101,9 @@ layernorm_row_kernel(const float* __restrict__ x, int64_t ldx, const int* __rest
     if (j < nv) { load4(gamma + 4 * j, g[i]); load4(beta + 4 * j, bt[i]); }
   }
   pdl_wait();
+  // optional: clear row r of an fp32 buffer that the next product accumulates into (K-split partial sums)
+  if (zero)
+    for (int j = tid; j < (nz >> 2); j += 128) reinterpret_cast<float4*>(zero + (int64_t)r * ldz)[j] = make_float4(0.f, 0.f, 0.f, 0.f);
   const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)(row_idx ? row_idx[r] : r) * ldx);
   float4 v[MAXI];
 #pragma unroll

@@ -107,6 +107,7 @@ struct wdz_engine {
   TsParams ts_params{50257, 50365, 51865, 50, 100, 1u, 2u};
   int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
   int sw_bm64 = 0;            // 64-feature tiles for the complete-sum decode products (tuning experiments)
+  int split_cross_q = 1;      // cross-attention query product as K-split sums into a cleared buffer
   int row_tile_override = 0;  // > 0: row tile of the decode products (32..256; tuning experiments)
   int ksplit_override = 0;  // > 0: fixed K split of the residual decode products (tuning experiments)
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
@@ -297,11 +298,12 @@ int dec_gemm(wdz_engine* e, int epi, const float* x, int64_t ldx, const void* W,
 
 template <typename TP, typename TO>
 int launch_ln(wdz_engine* e, const float* x, int64_t ldx, const int* row_idx, const void* g, const void* b,
-              TO* y, int64_t ldy, int rows, int d, cudaStream_t s) {
+              TO* y, int64_t ldy, int rows, int d, cudaStream_t s, float* zero = nullptr, int64_t ldz = 0, int nz = 0) {
   if (rows <= 0) return WDZ_OK;
+  if (zero && (rows > 1024 || (nz & 3) || (ldz & 3))) return e->fail(WDZ_EINVAL, "layernorm: cannot clear %d x %d", rows, nz);
   if (rows <= 1024)   // few rows: a CTA per row (latency-bound); many rows: a warp per row (bandwidth-bound)
     launch_pdl(e, layernorm_row_kernel<TP, TO>, dim3(rows), dim3(128), 0, s, x, ldx, row_idx, (const TP*)g,
-               (const TP*)b, y, ldy, rows, d);
+               (const TP*)b, y, ldy, rows, d, zero, ldz, nz);
   else
   launch_pdl(e, layernorm_kernel<TP, TO>, dim3((rows + 3) / 4), dim3(128), 0, s, x, ldx, row_idx, (const TP*)g, (const TP*)b, y, ldy, rows, d);
   WDZ_LAUNCH_CHECK(e, "layernorm");
@@ -530,8 +532,12 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
     if ((rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
     if ((rc = gemm(EPI_RESID, ao, d, w.out_w, w.out_b, e->dx, d, n, d, d, w.xq_w, wb))) return rc;
 
-    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s))) return rc;
-    if ((rc = gemm(EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, w.xout_w, wb))) return rc;
+    // The cross-attention query is a complete-sum product of only d features: as such it would stream its
+    // weights through a tenth of the SMs.  Its LayerNorm clears the query buffer instead and the product runs as
+    // K-split partial sums added into it, like the residual products.
+    const bool split_q = kBf16 && n > e->gemv_max_rows && n <= 1024 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE) && e->split_cross_q;
+    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s, split_q ? e->dq : nullptr, d, d))) return rc;
+    if ((rc = gemm(split_q ? EPI_RESID : EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, w.xout_w, wb))) return rc;
     if (cap) {
       int here = 0;
       for (int j = 0; j < e->al_heads.n; ++j) here += e->al_heads.layer[j] == l;
@@ -789,6 +795,7 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
   e->esz = c.dtype == WDZ_BF16 ? 2 : 4;
   if (const char* ks = getenv("WDZ_KSPLIT")) e->ksplit_override = atoi(ks);
   if (const char* rt = getenv("WDZ_ROWTILE")) e->row_tile_override = atoi(rt) / 32 * 32;
+  if (const char* sq = getenv("WDZ_SPLIT_CROSS_Q")) e->split_cross_q = atoi(sq);
   if (const char* b64 = getenv("WDZ_SW_BM64")) e->sw_bm64 = atoi(b64);
   if (const char* gm = getenv("WDZ_GEMV_MAX_ROWS")) e->gemv_max_rows = atoi(gm);
   e->enc.resize(c.n_audio_layer);
