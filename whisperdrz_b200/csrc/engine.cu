@@ -1580,7 +1580,15 @@ int wdz_align_matrix(wdz_engine* e, const int32_t* tokens_dev, const int32_t* ch
 #endif
   // the row-wise pass appends to the self-attention rows of the chunks' slots from position 0
   if (!tc_pass) reset_seqlens_kernel<<<(n_chunks + 255) / 256, 256, 0, st>>>(chunk_slots_dev, e->seq_lens, n_chunks, c.n_slots);
-  const int64_t group = tc_pass ? (int64_t)(c.max_rows / t_pad) * t_pad : c.max_rows;
+  // rows per forward call: whole chunks, and for the tensor-core pass no more 128-row tiles than make the
+  // d-wide products (d / 256 column tiles each) one full wave of the SMs; 3d- and 4d-wide ones then take 3 and 4
+  int64_t group = c.max_rows;
+  if (tc_pass) {
+    const int64_t wave_rows = (int64_t)std::max(1, e->sm_count / std::max(1, c.n_text_state / 256)) * 128;
+    int64_t cap_rows = std::min<int64_t>(c.max_rows, wave_rows);
+    if (cap_rows < t_pad) cap_rows = t_pad;
+    group = cap_rows / t_pad * t_pad;
+  }
   for (int64_t r0 = 0; r0 < rows; r0 += group) {
     const int n = (int)(rows - r0 < group ? rows - r0 : group);
     align_rows_kernel<<<(n + 255) / 256, 256, 0, st>>>(chunk_slots_dev, chunk_lens_dev, t_pad, (int)r0, n, c.n_slots, e->al_slots, e->al_pos);
