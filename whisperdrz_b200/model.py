@@ -90,7 +90,7 @@ class B200Model:
         """model.py:773-811: builds the engine (it owns the caches) and returns per-layer views."""
         self.engine = Engine(self.dims, self._sd, dtype=self._dtype, device=self._device, n_slots=batch_size,
                              max_tokens=max_tokens or self.dims.n_text_ctx, max_clips=self._max_clips,
-                             max_rows=max(64, batch_size * 8))
+                             max_rows=max(64, batch_size * 8, self.dims.n_text_ctx))   # >= one alignment chunk
         e = self.engine
         L = self.dims.n_text_layer
         H = self.dims.n_text_head
