@@ -25,7 +25,10 @@ def load_model(name_or_path="large-v3", lang: str | None = "en", dtype=None, dev
     name_or_path: a shape name known to ``ModelDimensions.from_name`` (weights
     are then drawn from ``seed``; released checkpoints are not reachable
     offline), or a path to a ``.pt`` / ``.safetensors`` state_dict with the
-    reference's tensor names (large-v3 shapes)."""
+    reference's tensor names (large-v3 shapes).  ``dtw_align=True`` (the
+    reference's default, transcriber.py:525) adds word timing of every finished
+    window at token level (``alignment.token_aligner``; pass ``aligner=`` for a
+    tokenizer-aware one): results then carry ``word_times``."""
     import os
 
     import torch
@@ -49,6 +52,11 @@ def load_model(name_or_path="large-v3", lang: str | None = "en", dtype=None, dev
     else:
         dims = ModelDimensions.from_name(name_or_path)
         sd = init_state_dict(dims, seed)
-    engine = Engine(dims, sd, dtype=dtype, device=device, n_slots=n_slots, max_clips=max_clips,
+    if kwargs.pop("dtw_align", False) and "aligner" not in kwargs:
+        from .alignment import token_aligner
+        kwargs["aligner"] = token_aligner
+    # with alignment on, room for whole chunks in one forward call (the pass then runs on the tensor cores)
+    max_rows = max(n_slots, 64, 4096 if kwargs.get("aligner") is not None else 0)
+    engine = Engine(dims, sd, dtype=dtype, device=device, n_slots=n_slots, max_clips=max_clips, max_rows=max_rows,
                     tables=timestamp_tables(dims.n_vocab))
     return Transcriber(engine, lang=lang, **kwargs)
