@@ -146,3 +146,28 @@ def test_tensor_core_pass_matches_row_wise_pass_on_long_chunks(gold):
     for b in range(2):
         diff = (out[0][b, : lens[b], : max(caps)] - m[b, : lens[b]]).abs()
         assert diff.mean() < 0.02 and diff.max() < 0.5, (float(diff.mean()), float(diff.max()))
+
+
+def test_load_model_with_word_timing_end_to_end():
+    """load_model(dtw_align=True): every finished window is aligned on the engine before its slot is reused;
+    chunks carry one (token index, start, end) per text token, inside the chunk's time range, and the token
+    ids are the same as without alignment (the pass must not disturb decoding)."""
+    import whisperdrz_b200
+    from whisperdrz_b200.dims import TOK_EOT
+    audio = torch.from_numpy(synth.long_form(3, 70.0))
+    out = {}
+    for align in (False, True):
+        t = whisperdrz_b200.load_model("test-small", n_slots=2, max_clips=2, dtype=torch.float32, max_new_tokens=40,
+                                       dtw_align=align, align_heads=[(0, 1), (1, 0), (1, 3)])
+        out[align] = t.transcribe(audio)
+        t.engine.device_status()
+        if align:
+            assert t.windows_aligned >= len(out[align].raw_chunks) == 3
+        t.engine.close()
+    for a, b in zip(out[False].raw_chunks, out[True].raw_chunks):
+        assert a["tokens"] == b["tokens"] and a["stop_reason"] == b["stop_reason"]
+        words = b["word_times"]
+        text_pos = [i for i, tk in enumerate(b["tokens"]) if tk < TOK_EOT]
+        assert sorted(w[0] for w in words) == [w[0] for w in words] and set(w[0] for w in words) <= set(text_pos)
+        assert len(words) >= 1
+        assert all(b["offset"] - 1e-6 <= w[1] <= w[2] <= b["offset"] + 30.0 + 1e-6 for w in words)
