@@ -150,17 +150,19 @@ def test_sharding_is_a_partition():
 WORKER = r"""
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
-from test_scheduler_cpu import StubEngine, _patch_rules_dev
+from test_scheduler_cpu import AlignStubEngine, _patch_rules_dev
+from whisperdrz_b200.alignment import token_aligner
 from whisperdrz_b200.transcriber import Transcriber
 from whisperdrz_b200.sharding import transcribe_sharded
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
-tr = Transcriber(StubEngine(), max_new_tokens=20); _patch_rules_dev(tr)
+tr = Transcriber(AlignStubEngine(), max_new_tokens=20, aligner=token_aligner); _patch_rules_dev(tr)
 torch.manual_seed(0)
 audio = torch.randn(16000 * 30 * 7)
 res = transcribe_sharded(tr, audio, rank, world)
 if rank == 0:
     assert [r["id"] for r in res.raw_chunks] == [f"chunk_{i}" for i in range(7)], res.raw_chunks
+    assert all(len(r["word_times"]) >= 1 for r in res.raw_chunks)      # word timing travels with the gathered chunks
     print("GATHERED", len(res.raw_chunks), len(res.segments))
 else:
     assert res is None
