@@ -10,7 +10,9 @@ them and records small slices of what they compute on the seeded synthetic
 clips of ``whisperdrz_b200.synth``.  Only slices are stored (a few hundred KB);
 the slicing pattern is stored with them.  ``--large`` adds the full-size
 large-v3 case (224 greedy tokens from a 4-token prompt with EOS suppressed);
-it needs about 14 GB of RAM and a few minutes of CPU.
+it needs about 14 GB of RAM and a few minutes of CPU.  ``--large-rows`` records
+the full-size ragged multi-row decode case (32 slots, prompts of 4..420 tokens,
+24 teacher-forced steps; see ``rows_golden``); about 25 GB of RAM.
 """
 from __future__ import annotations
 
@@ -105,10 +107,80 @@ def model_golden(name: str, n_steps: int, seed: int = 0, clip_seeds=(1,), logit_
     return out
 
 
+ROWS_N, ROWS_STEPS, ROWS_GROUP, ROWS_STRIDE = 32, 24, 8, 97
+
+
+def rows_inputs(n_rows: int = ROWS_N, seed: int = 2):
+    """Seeded inputs of the ragged multi-row case, shared with the GPU test:
+    encoder states xa_i ~ N(0, 1) [1500, d] (seed 100 + i), prompt lengths
+    U{4..64} with ids U{0..49999} (``synth.decode_lengths``), except that the last
+    four rows carry 150/250/350/420-token prompts so that deep caches are covered."""
+    p, _, prompts = synth.decode_lengths(seed, n_rows)
+    rng = np.random.default_rng(seed + 1)
+    for j, n in enumerate((150, 250, 350, 420)):
+        prompts[n_rows - 4 + j] = rng.integers(0, 50000, n).astype(np.int64)
+    return prompts
+
+
+def rows_xa(i: int, d: int) -> torch.Tensor:
+    g = torch.Generator(device="cpu")
+    g.manual_seed(100 + i)
+    return torch.empty(1500, d, dtype=torch.float32).normal_(0.0, 1.0, generator=g)
+
+
+@torch.inference_mode()
+def rows_golden(name: str = "large-v3", seed: int = 0):
+    """The batched ragged decode of the throughput benchmark at full size, from
+    the unmodified reference on CPU in fp32: every row is prefilled on its own
+    (the reference's ``prefill_flash`` takes rectangular prompts), then
+    ``ROWS_STEPS`` decode steps run ``ROWS_GROUP`` rows at a time through
+    ``decoder.forward_flash`` at each row's own depth.  The token fed at every step
+    is the reference's greedy choice (EOS suppressed) and is stored, so that the
+    engine can be teacher-forced with it.  Stored per (row, step): every
+    ``ROWS_STRIDE``-th logit, the full-row RMS and the arg-max id."""
+    dims = ModelDimensions.from_name(name)
+    m = ref_model(dims, seed)
+    m.decoder.cache_embedding_weight(torch.float32)
+    prompts = rows_inputs()
+    eot = min(TOK_EOT, dims.n_vocab - 1)
+    n_keep = len(range(0, dims.n_vocab, ROWS_STRIDE))
+    logits_k = np.zeros((ROWS_N, ROWS_STEPS + 1, n_keep), np.float32)
+    rms = np.zeros((ROWS_N, ROWS_STEPS + 1), np.float64)
+    fed = np.zeros((ROWS_N, ROWS_STEPS + 1), np.int64)
+    t0 = time.time()
+    for g0 in range(0, ROWS_N, ROWS_GROUP):
+        rows = list(range(g0, g0 + ROWS_GROUP))
+        self_kv, cross_kv = m.create_flash_kv(ROWS_GROUP, max_tokens=dims.n_text_ctx)
+        cur = []
+        for j, r in enumerate(rows):
+            xa = rows_xa(r, dims.n_audio_state)[None]
+            pr = torch.from_numpy(prompts[r])[None]
+            lg = m.prefill_flash(pr, xa, self_kv, cross_kv, torch.tensor([j]))[0, -1]
+            cur.append(lg)
+        logits = torch.stack(cur)
+        slots = torch.arange(ROWS_GROUP)
+        for step in range(ROWS_STEPS + 1):
+            logits_k[rows, step] = logits[:, ::ROWS_STRIDE].numpy()
+            rms[rows, step] = logits.double().pow(2).mean(-1).sqrt().numpy()
+            lg = logits.clone()
+            lg[:, eot] = float("-inf")
+            nxt = lg.argmax(-1)
+            fed[rows, step] = nxt.numpy()
+            if step == ROWS_STEPS:
+                break
+            pos = self_kv[0].seq_lens[slots]
+            logits = m.decoder.forward_flash(nxt[:, None], self_kv, cross_kv, pos, slot_indices=slots)[:, 0]
+        print(f"rows {g0}..{g0 + ROWS_GROUP - 1}: {time.time() - t0:.1f}s", flush=True)
+        del self_kv, cross_kv
+    return {"seed": np.int64(seed), "stride": np.int64(ROWS_STRIDE), "logits": logits_k, "rms": rms,
+            "tokens": fed, "prompt_lens": np.asarray([len(p) for p in prompts])}
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--large", action="store_true")
     ap.add_argument("--skip-small", action="store_true")
+    ap.add_argument("--large-rows", action="store_true")
     args = ap.parse_args()
     torch.manual_seed(0)
     if not args.skip_small:
@@ -121,4 +193,6 @@ if __name__ == "__main__":
         np.savez_compressed(os.path.join(HERE, "model_large_v3_cfg1.npz"),
                             **model_golden("large-v3", 224, clip_seeds=(1,), logit_stride=997,
                                            keep_steps=(0, 1, 2, 50, 100, 150, 223)))
+    if args.large_rows:
+        np.savez_compressed(os.path.join(HERE, "model_large_v3_rows.npz"), **rows_golden())
     print("done")

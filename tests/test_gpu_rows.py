@@ -1,0 +1,177 @@
+"""The batched ragged decode at full size (Whisper-large-v3 shapes) against the
+reference's own recording (tests/golden/make_golden.py --large-rows): 32 slots
+with prompts of 4..420 tokens, 24 teacher-forced decode steps.
+
+This is the configuration the throughput benchmark and the 32-slot decode case
+run: more than 16 rows per step take the operand-swapped tcgen05 products with
+K splits, the split cross-attention query product, the multi-way split
+cross-attention and the captured step graph.  Tolerances as everywhere: bf16
+teacher-forced logits within 3e-2 x the row's logit RMS (max-abs), fp32 greedy
+token ids identical."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from whisperdrz_b200.dims import ModelDimensions, TOK_EOT
+from whisperdrz_b200.rules import BatchRuleState, timestamp_tables
+from whisperdrz_b200.weights import init_state_dict
+
+pytestmark = pytest.mark.gpu
+
+BF16_LOGIT_TOL = 3e-2
+N_ROWS = 32
+
+
+def rows_inputs(n_rows: int = N_ROWS, seed: int = 2):
+    """Same draws as tests/golden/make_golden.py:rows_inputs."""
+    from whisperdrz_b200 import synth
+    _, _, prompts = synth.decode_lengths(seed, n_rows)
+    rng = np.random.default_rng(seed + 1)
+    for j, n in enumerate((150, 250, 350, 420)):
+        prompts[n_rows - 4 + j] = rng.integers(0, 50000, n).astype(np.int64)
+    return prompts
+
+
+def rows_xa(i: int, d: int) -> torch.Tensor:
+    g = torch.Generator(device="cpu")
+    g.manual_seed(100 + i)
+    return torch.empty(1500, d, dtype=torch.float32).normal_(0.0, 1.0, generator=g)
+
+
+@pytest.fixture(scope="module")
+def large():
+    dims = ModelDimensions.from_name("large-v3")
+    return dims, init_state_dict(dims, 0)
+
+
+@pytest.fixture(scope="module")
+def golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "model_large_v3_rows.npz"))
+    prompts = rows_inputs()
+    assert [len(p) for p in prompts] == [int(n) for n in g["prompt_lens"]]
+    return g, prompts
+
+
+def _prefill(e, dims, prompts, slot0: int = 0):
+    """Cross K/V + prompt rows of the 32 recorded slots, 8 windows per call; returns the last-prompt-token logits."""
+    out = []
+    for g0 in range(0, N_ROWS, 8):
+        xa = torch.stack([rows_xa(r, dims.n_audio_state) for r in range(g0, g0 + 8)]).cuda()
+        out.append(e.prefill(xa, [slot0 + r for r in range(g0, g0 + 8)],
+                             [[int(t) for t in prompts[r]] for r in range(g0, g0 + 8)]))
+    return torch.cat(out)
+
+
+def _worst(logits, g, step, stride):
+    """max over rows of max-abs(logits - recorded) / recorded row RMS; row r is compared with recorded row r % 32."""
+    ref = torch.from_numpy(g["logits"][:, step])
+    rms = torch.from_numpy(g["rms"][:, step]).float()
+    got = logits[:, ::stride].float().cpu()
+    reps = got.shape[0] // N_ROWS
+    err = (got.view(reps, N_ROWS, -1) - ref[None]).abs().amax(-1) / rms[None]
+    return float(err.max())
+
+
+def _replicate(e, prompts, n_copies):
+    """Slots 32.. become copies of the prefilled slots 0..31 (caches and lengths)."""
+    for j in range(1, n_copies + 1):
+        lo = N_ROWS * j
+        for t in (e.self_k, e.self_v, e.cross_k, e.cross_v):
+            t[:, lo: lo + N_ROWS].copy_(t[:, :N_ROWS])
+        e.seq_lens_dev[lo: lo + N_ROWS] = e.seq_lens_dev[:N_ROWS]
+
+
+def test_large_v3_bf16_ragged_rows_32_and_256(large, golden):
+    """(1) 32 ragged rows per step and (2) 256 rows per step (the 32 recorded slots replicated eight times:
+    every replica must reproduce its recorded row) through wdz_prefill + the wdz_decode_step graph."""
+    from whisperdrz_b200.engine import Engine
+    dims, sd = large
+    g, prompts = golden
+    stride = int(g["stride"])
+    steps = g["tokens"].shape[1] - 1
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=N_ROWS * 9, max_clips=8, max_rows=1280,
+               tables=timestamp_tables(dims.n_vocab))
+    logits0 = _prefill(e, dims, prompts)
+    worst = _worst(logits0, g, 0, stride)
+    assert worst < BF16_LOGIT_TOL, ("prefill", worst)
+    assert e.seq_lens()[:N_ROWS] == [len(p) for p in prompts]
+    _replicate(e, prompts, 8)
+    fed = torch.from_numpy(g["tokens"])
+    slots32 = list(range(N_ROWS))
+    slots256 = list(range(N_ROWS, N_ROWS * 9))
+    for step in range(steps):
+        _, lg = e.decode_step(fed[:, step], slots32, want_logits=True)
+        worst = max(worst, _worst(lg, g, step + 1, stride))
+        _, lg = e.decode_step(fed[:, step].repeat(8), slots256, want_logits=True)
+        worst = max(worst, _worst(lg, g, step + 1, stride))
+        assert worst < BF16_LOGIT_TOL, (step, worst)
+    e.device_status()
+    lens = e.seq_lens()
+    assert lens[:N_ROWS] == [len(p) + steps for p in prompts]
+    assert lens[N_ROWS:] == lens[:N_ROWS] * 8
+
+    # (3) rule state kept on the device (wdz_ts_first / wdz_ts_steps, several steps per host round trip) at
+    # 256 rows against the same engine stepped from the host with the same token-level rules: rewind the
+    # slots to their prompts, decode 16 tokens each way, ids must be identical.
+    n_new = 16
+    lens0 = torch.tensor([len(p) for p in prompts] * 9, dtype=torch.int32).cuda()
+    first = logits0.repeat(8, 1)
+
+    def host_path():
+        e.seq_lens_dev.copy_(lens0)
+        rs = BatchRuleState(N_ROWS * 9, n_new)
+        toks = {s: [] for s in slots256}
+        active = list(slots256)
+        cur = e.rules_argmax(first, torch.from_numpy(rs.rules_array(np.asarray(active))).cuda()).tolist()
+        for i in range(n_new):
+            done = rs.update(np.asarray(active), cur)
+            for s, t in zip(active, cur):
+                toks[s].append(int(t))
+            keep = [j for j, d in enumerate(done) if not d]
+            active, cur = [active[j] for j in keep], [cur[j] for j in keep]
+            if not active or i == n_new - 1:
+                break
+            cur = e.decode_step(cur, active, rules=torch.from_numpy(rs.rules_array(np.asarray(active))).cuda()).tolist()
+        return toks
+
+    def device_path():
+        e.seq_lens_dev.copy_(lens0)
+        e.ts_reset(slots256, [n_new] * len(slots256))
+        e.ts_first(first, slots256)
+        e.ts_steps(slots256, 5)
+        e.ts_steps(slots256, n_new - 5 - 1)
+        st = e.ts_poll()
+        return {s: e.ts_tokens(s, int(st[s][1])) for s in slots256}
+
+    a, b = host_path(), device_path()
+    assert a == b
+    assert all(len(a[s]) == n_new or a[s][-1] == TOK_EOT for s in slots256)
+    assert [a[s] for s in slots256[:N_ROWS]] == [a[s] for s in slots256[N_ROWS: 2 * N_ROWS]]   # replicas decode alike
+    e.device_status()
+    e.close()
+
+
+def test_large_v3_fp32_ragged_rows_tokens_identical(large, golden):
+    """fp32 engine, free-running greedy decode of the 32 ragged rows with EOS suppressed: the 25 token ids of
+    every row equal the reference's."""
+    from whisperdrz_b200.engine import Engine
+    dims, sd = large
+    g, prompts = golden
+    stride = int(g["stride"])
+    steps = g["tokens"].shape[1] - 1
+    e = Engine(dims, sd, dtype=torch.float32, n_slots=N_ROWS, max_clips=8, max_rows=1280)
+    logits = _prefill(e, dims, prompts)
+    rule = [{"set_ids": [TOK_EOT]}] * N_ROWS
+    cur = e.rules_argmax(logits, rule)
+    toks = [cur.cpu()]
+    worst = _worst(logits, g, 0, stride)
+    for step in range(steps):
+        cur, logits = e.decode_step(cur, list(range(N_ROWS)), rules=rule, want_logits=True)
+        toks.append(cur.cpu())
+        worst = max(worst, _worst(logits, g, step + 1, stride))
+    e.device_status()
+    assert np.array_equal(torch.stack(toks, 1).numpy(), g["tokens"])
+    assert worst < 1e-3, worst
+    e.close()
