@@ -220,9 +220,7 @@ def main():
     ap.add_argument("--clips", type=int, default=256, help="30 s chunks per GPU per step")
     ap.add_argument("--new-tokens", type=int, default=224)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--host-rules", action="store_true", help="rule state on the host, one decode step per round trip")
     ap.add_argument("--steps-per-poll", type=int, default=8)
-    ap.add_argument("--engine-flags", type=int, default=0, help="WDZ_FLAG_* bits (A/B runs)")
     ap.add_argument("--align", action="store_true",
                     help="also run the DTW word-timing alignment on every finished window (token-level words); "
                          "not part of the headline workload, named in config.workload when on")
@@ -250,14 +248,14 @@ def main():
     dims = ModelDimensions.from_name(args.model)
     sd = init_state_dict(dims, 0)
     eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(16, args.clips),
-                 flags=args.engine_flags, max_rows=max(args.clips, 64, 4096 if args.align else 0),
+                 max_rows=max(args.clips, 64, 4096 if args.align else 0),
                  tables=timestamp_tables(dims.n_vocab))
     audio_host = torch.from_numpy(synth.clips([1000 * rank + i + 1 for i in range(args.clips)])).pin_memory()
     audio_dev = audio_host.to(dev)
 
     def one_step(src):
         tr = Transcriber(eng, max_new_tokens=args.new_tokens, max_continuations=0,
-                         device_rules=not args.host_rules, steps_per_poll=args.steps_per_poll,
+                         device_rules=True, steps_per_poll=args.steps_per_poll,
                          aligner=token_aligner if args.align else None)
         for i in range(args.clips):
             tr.pending_chunks.append({"audio": src[i], "id": f"chunk_{i}", "duration": 30.0, "offset": 0.0})
@@ -283,6 +281,7 @@ def main():
             dsteps += tr.steps
         b.record()
         torch.cuda.synchronize()
+        eng.device_status()        # raises if any kernel of the timed steps reported an error: no number then
         ms = torch.tensor([a.elapsed_time(b)], device=dev)
         if world > 1:
             dist.barrier()

@@ -1,7 +1,7 @@
 """Timings of the named workloads other than the batched end-to-end case that
 bench.py times, on one GPU:
 
-    python -m whisperdrz_b200.configs [cfg1 cfg2 cfg3 cfg5 align align_small products products_once]
+    python bench_configs.py [cfg1 cfg2 cfg3 cfg5 align align_small products products_once]
 
 cfg1  one 30 s clip, 4-token prompt, 224 greedy tokens with EOS suppressed (latency; fp32 and bf16)
 cfg2  encoder only, bf16, 16 clips: log-mel + conv stem + 32 layers (time, TFLOP/s)
@@ -26,12 +26,16 @@ import time
 import numpy as np
 import torch
 
-from . import synth
-from .dims import ModelDimensions, TOK_EOT
-from .engine import Engine
-from .rules import timestamp_tables
-from .transcriber import Transcriber
-from .weights import init_state_dict
+import os
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from whisperdrz_b200 import synth  # noqa: E402
+from whisperdrz_b200.dims import ModelDimensions, TOK_EOT  # noqa: E402
+from whisperdrz_b200.engine import Engine  # noqa: E402
+from whisperdrz_b200.rules import timestamp_tables  # noqa: E402
+from whisperdrz_b200.transcriber import Transcriber  # noqa: E402
+from whisperdrz_b200.weights import init_state_dict  # noqa: E402
 
 ENC_GFLOP_PER_CLIP = 2274.0  # conv 17.7 + 32 x (59.0 GEMM + 11.5 attention)
 
@@ -173,7 +177,7 @@ def cfg5(dims, sd, n_req=96, slots=256, seed=4, min_refill=1):
 
 
 def align(dims, sd, n_chunks=8, n_ids=440, reps=3):
-    from . import alignment as A
+    from whisperdrz_b200 import alignment as A
     e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=n_chunks, max_clips=8, max_rows=4096)
     g = torch.Generator(device="cpu").manual_seed(6)
     xa = (torch.randn(n_chunks, dims.n_audio_ctx, dims.n_audio_state, generator=g) * 0.5).to(torch.bfloat16).cuda()

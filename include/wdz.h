@@ -237,7 +237,9 @@ int wdz_ts_first(wdz_engine* e, const float* logits_dev, const int32_t* slot_ids
  * updates its state and appends the token to its log.  Finished slots keep producing EOT until dropped. */
 int wdz_ts_steps(wdz_engine* e, const int32_t* slot_ids_dev, int n, int k, wdz_stream s);
 /* Copies all slot states to host (24 x int32 per slot: max_new, n_new, timing_count, last_timing,
- * last_was_timing, n_recent, done, last_token, recent[10], 6 spare).  Synchronises the stream. */
+ * last_was_timing, n_recent, done, last_token, recent[10], 6 spare).  Synchronises the stream.
+ * The device status word is read in the same round trip: when a kernel since the last poll gave up a
+ * bounded wait or met a NaN logits row, the call returns that code (WDZ_ETIMEOUT, WDZ_ENAN) and clears it. */
 int wdz_ts_poll(wdz_engine* e, int32_t* out_host, wdz_stream s);
 /* Copies the first cap generated tokens of one slot to host.  Synchronises the stream. */
 int wdz_ts_tokens(wdz_engine* e, int slot, int32_t* out_host, int cap, wdz_stream s);

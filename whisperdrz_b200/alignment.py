@@ -65,69 +65,76 @@ def build_full_tokens(ids_list: list[list[int]], sot_sequence=SOT_SEQUENCE, no_t
 
 def anchor_row_limits(n_rows: int, n_cols: int, word_lens: list[int],
                       word_anchors=None, tag_anchors=None, slack_frames: int = 7) -> tuple[np.ndarray, np.ndarray]:
-    """Allowed audio columns [lo, hi) of each text row of the cost matrix.
+    """Allowed audio columns [lo, hi) of each text row of the cost matrix, as two int32 arrays.
 
-    The reference sets cost to +inf outside bands around the timestamps the
-    decoder itself emitted: rows of an anchored word may only use columns
-    within ``slack_frames`` of its (start, end); the last row of the word
-    before a speaker tag must end before the tag's end, the first row of the
-    word after it must start after the tag's start.  Several bands on one row
-    intersect.  Row 0 is the no-timestamps row, word w starts at row
-    ``1 + sum(word_lens[:w])``.  A band is skipped under the reference's
-    conditions (word index past the last word, non-increasing anchor end,
-    empty column or row range)."""
+    Where the decoder itself emitted timestamps, the reference forbids (cost +inf) everything outside
+    bands around them (dtw_align.py:589-641); the device DTW takes the same constraint as a column
+    interval per row, so nothing is written into the matrix.  Rows: row 0 is the no-timestamps token,
+    word w owns rows ``first[w] .. first[w + 1] - 1`` with ``first = 1 + exclusive cumsum(word_lens)``.
+
+    * a timed word (index, start, end) keeps its rows within ``slack_frames`` positions of
+      [start, end].  Anchors are honoured in list order only while their end times strictly increase;
+      an anchor is also void when its word index, its column span or its row span is empty.
+    * a timed tag (start, end, previous word, next word) makes the last row of the previous word end
+      before the tag's end and the first row of the next word start after the tag's start.
+    Several constraints on one row intersect."""
     lo = np.zeros(n_rows, dtype=np.int32)
     hi = np.full(n_rows, n_cols, dtype=np.int32)
-    n_words = len(word_lens)                       # the reference's word list has one more entry (the eot)
-    bounds = np.cumsum([1, *word_lens])            # first row of word w; bounds[n_words] = one past the last
-    bands: list[tuple[int, int, int | None, int | None]] = []
-    seen_max = -1.0
-    for wi, a_s, a_e in word_anchors or []:
-        wi = int(wi)
-        if wi >= n_words or a_e <= seen_max:
+    n_words = len(word_lens)
+    first = 1 + np.concatenate([[0], np.cumsum(word_lens)]).astype(np.int64)      # [n_words + 1]
+
+    def col(t):   # seconds -> audio position
+        return np.rint(np.asarray(t, dtype=np.float64) * TOKENS_PER_SECOND).astype(np.int64)
+
+    wa = np.asarray(word_anchors if word_anchors is not None and len(word_anchors) else np.zeros((0, 3)), dtype=np.float64).reshape(-1, 3)
+    if len(wa):
+        w = wa[:, 0].astype(np.int64)
+        c_lo = np.maximum(0, col(wa[:, 1]) - slack_frames)
+        c_hi = np.minimum(n_cols, col(wa[:, 2]) + slack_frames)
+        inside = w < n_words
+        wc = np.where(inside, w, 0)
+        r_lo, r_hi = first[wc], np.minimum(first[wc + 1], n_rows)
+        usable = inside & (c_lo < c_hi) & (r_lo < r_hi)
+        # "end times strictly increase": compare with the largest end among the usable anchors before it
+        ends = np.where(usable, wa[:, 2], -np.inf)
+        before = np.concatenate([[-1.0], np.maximum.accumulate(ends)[:-1]])
+        keep = usable & (wa[:, 2] > np.maximum(before, -1.0))
+        for k in np.nonzero(keep)[0]:
+            rows = slice(int(r_lo[k]), int(r_hi[k]))
+            if c_lo[k] > 0:
+                lo[rows] = np.maximum(lo[rows], c_lo[k])
+            if c_hi[k] < n_cols:
+                hi[rows] = np.minimum(hi[rows], c_hi[k])
+    for t_s, t_e, prev_w, next_w in tag_anchors or []:
+        c_lo = max(0, int(col(t_s)) - slack_frames)
+        c_hi = min(n_cols, int(col(t_e)) + slack_frames)
+        if c_hi <= 0 or c_lo >= n_cols:
             continue
-        a_lo = max(0, int(round(a_s * TOKENS_PER_SECOND)) - slack_frames)
-        a_hi = min(n_cols, int(round(a_e * TOKENS_PER_SECOND)) + slack_frames)
-        if a_lo >= a_hi:
-            continue
-        r_lo, r_hi = int(bounds[wi]), min(int(bounds[wi + 1]), n_rows)
-        if r_lo >= r_hi:
-            continue
-        bands.append((r_lo, r_hi, a_lo, a_hi))
-        seen_max = a_e
-    for a_s, a_e, p_local, n_local in tag_anchors or []:
-        a_lo = max(0, int(round(a_s * TOKENS_PER_SECOND)) - slack_frames)
-        a_hi = min(n_cols, int(round(a_e * TOKENS_PER_SECOND)) + slack_frames)
-        if a_hi <= 0 or a_lo >= n_cols:
-            continue
-        if p_local is not None and int(p_local) < n_words:
-            r = min(int(bounds[int(p_local) + 1]) - 1, n_rows - 1)
+        if prev_w is not None and int(prev_w) < n_words and c_hi < n_cols:
+            r = min(int(first[int(prev_w) + 1]) - 1, n_rows - 1)
             if r >= 0:
-                bands.append((r, r + 1, None, a_hi))
-        if n_local is not None and int(n_local) < n_words:
-            r = min(int(bounds[int(n_local)]), n_rows - 1)
+                hi[r] = min(hi[r], c_hi)
+        if next_w is not None and int(next_w) < n_words and c_lo > 0:
+            r = min(int(first[int(next_w)]), n_rows - 1)
             if r >= 0:
-                bands.append((r, r + 1, a_lo, None))
-    for r_lo, r_hi, a_lo, a_hi in bands:
-        if a_lo is not None and a_lo > 0:
-            lo[r_lo:r_hi] = np.maximum(lo[r_lo:r_hi], a_lo)
-        if a_hi is not None and a_hi < n_cols:
-            hi[r_lo:r_hi] = np.minimum(hi[r_lo:r_hi], a_hi)
+                lo[r] = max(lo[r], c_lo)
     return lo, hi
 
 
 def word_times_from_path(text_idx: np.ndarray, time_idx: np.ndarray, word_lens: list[int]) -> list[tuple[float, float]]:
-    """(start, end) seconds of each word: the audio position at which the path first enters the word's
-    first row, and the one at which it enters the next word's.  Empty when the path never reaches the last
-    boundary, as in the reference."""
+    """(start, end) seconds of each word from a DTW path (dtw_align.py:644-667).  The path visits the text
+    rows in order without skipping any, so the moment it enters row r is ``time_idx`` at the first path
+    step whose row is r; a word starts when the path enters its first row and ends when it enters the
+    next word's first row.  Empty when the path stops before the row after the last word."""
     if len(text_idx) == 0 or not word_lens:
         return []
-    boundaries = np.pad(np.cumsum(word_lens), (1, 0))
-    jumps = np.pad(np.diff(text_idx), (1, 0), constant_values=1).astype(bool)
-    jump_times = np.asarray(time_idx)[jumps] / TOKENS_PER_SECOND
-    if boundaries[-1] >= len(jump_times):
+    edges = np.concatenate([[0], np.cumsum(word_lens)]).astype(np.int64)     # first row of each word, and one past
+    text_idx = np.asarray(text_idx)
+    if edges[-1] > int(text_idx[-1]) - int(text_idx[0]):
         return []
-    return list(zip(jump_times[boundaries[:-1]].tolist(), jump_times[boundaries[1:]].tolist()))
+    entered = np.searchsorted(text_idx, text_idx[0] + edges, side="left")
+    t = np.asarray(time_idx)[entered] / TOKENS_PER_SECOND
+    return list(zip(t[:-1].tolist(), t[1:].tolist()))
 
 
 def token_aligner(tokens: list[int], ts_begin: int = 50365, ts_end: int = 51865, eot: int = TOK_EOT, max_tokens: int = 440) -> list[dict]:

@@ -26,8 +26,7 @@ def build(force: bool = False, verbose: bool = False, extra: list[str] | None = 
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-shared", "-Xcompiler", "-fPIC", "--use_fast_math=false"]
-    cmd = [c for c in cmd if c != "--use_fast_math=false"]
+           "-shared", "-Xcompiler", "-fPIC"]
     if os.path.exists(os.path.join(CSRC, "gemm_tc.cuh")):
         cmd += ["-DWDZ_WITH_TC"]
     if verbose:

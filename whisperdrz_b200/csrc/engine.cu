@@ -105,11 +105,7 @@ struct wdz_engine {
   TsState* ts_state = nullptr;                       // [n_slots]
   int* ts_log = nullptr;                             // [n_slots, max_tokens] generated tokens per slot
   TsParams ts_params{50257, 50365, 51865, 50, 100, 1u, 2u};
-  int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
-  int sw_bm64 = 0;            // 64-feature tiles for the complete-sum decode products (tuning experiments)
-  int split_cross_q = 1;      // cross-attention query product as K-split sums into a cleared buffer
-  int row_tile_override = 0;  // > 0: row tile of the decode products (32..256; tuning experiments)
-  int ksplit_override = 0;  // > 0: fixed K split of the residual decode products (tuning experiments)
+  static constexpr int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
 
   // optional per-kernel timing (wdz_profile): event pairs around selected launches
@@ -492,6 +488,8 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
   ap.n_slots = c.n_slots; ap.d = d; ap.slots = slots;
   ap.part_o = e->part_o; ap.part_ml = e->part_ml; ap.out = ao; ap.ldo = d;
   // y = epi(x W^T + b) with x in T; RESID accumulates into the fp32 residual stream
+  // next_w / next_bytes: the weights the following product will stream; the small-row kernel (<= 16 rows) pulls a
+  // share of them into L2 while it runs, the many-row tcgen05 kernel ignores them
   auto gemm = [&](int epi, const T* x, int64_t ldx, const void* W, const void* bias, void* y, int64_t ldy, int M,
                   int N, int K, const void* next_w = nullptr, size_t next_bytes = 0) -> int {
     if constexpr (kBf16) {
@@ -535,7 +533,7 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
     // The cross-attention query is a complete-sum product of only d features: as such it would stream its
     // weights through a tenth of the SMs.  Its LayerNorm clears the query buffer instead and the product runs as
     // K-split partial sums added into it, like the residual products.
-    const bool split_q = kBf16 && n > e->gemv_max_rows && n <= 1024 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE) && e->split_cross_q;
+    const bool split_q = kBf16 && n > e->gemv_max_rows && n <= 1024 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE);
     if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s, split_q ? e->dq : nullptr, d, d))) return rc;
     if ((rc = gemm(split_q ? EPI_RESID : EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, w.xout_w, wb))) return rc;
     if (cap) {
@@ -697,15 +695,10 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   //  - residual sums (K split, red.global.add): a single row tile when K is long (operand bytes dominate),
   //    else 64- or 128-row tiles, and as many K splits as fill the wave.
   const int mpad_all = (g.M + 31) / 32 * 32;
-  // complete-sum products have one weight stream per feature tile: 64-feature tiles double the streams
-  const int bm = (epi != EPI_RESID && e->sw_bm64) ? 64 : tc::BM;
-  p.bm = bm;
-  const int tiles = (g.N + bm - 1) / bm;
+  const int tiles = (g.N + tc::BM - 1) / tc::BM;
   p.kblocks = g.K / tc::BK;
   int row_tile = mpad_all;
-  if (e->row_tile_override > 0) {
-    row_tile = std::min(mpad_all, e->row_tile_override);
-  } else if (epi == EPI_RESID) {
+  if (epi == EPI_RESID) {
     if (p.kblocks < 64) row_tile = std::min(mpad_all, g.M <= 128 ? 64 : 128);
   } else {
     for (int rt = 32; rt < mpad_all; rt *= 2)
@@ -718,27 +711,24 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   int ksplit = 1;
   if (epi == EPI_RESID) {
     ksplit = e->sm_count / (tiles * row_tiles);
-    if (e->ksplit_override > 0) ksplit = e->ksplit_override;
     if (ksplit > p.kblocks) ksplit = p.kblocks;
     if (ksplit < 1) ksplit = 1;
   }
   p.kb_per_split = (p.kblocks + ksplit - 1) / ksplit;
   ksplit = (p.kblocks + p.kb_per_split - 1) / p.kb_per_split;
   p.epi = epi == EPI_QKV_CACHE ? tc::EPI_SW_QKV_CACHE : epi;
-  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mpad >> 3) << 17) | ((uint32_t)(bm >> 4) << 24);
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mpad >> 3) << 17) | ((uint32_t)(tc::BM >> 4) << 24);
   p.cache_k = g.cache_k; p.cache_v = g.cache_v; p.slots = g.slots; p.positions = g.positions;
   p.layer = g.layer; p.n_slots = g.n_slots; p.S = g.S; p.d = g.d;
-  // (no L2 prefetch of the next weights here: measured slower at 32-256 rows, it competes with this
-  // kernel's own latency-bound TMA stream; the small-row kernel keeps it)
   p.status = e->status;
   CUtensorMap mw, mx;
-  if (!tc::make_map(&mw, g.W, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * g.N, (uint32_t)bm, 2))
+  if (!tc::make_map(&mw, g.W, (uint64_t)g.K, (uint64_t)g.N, 1, (uint64_t)g.K * 2, (uint64_t)g.K * 2 * g.N, (uint32_t)tc::BM, 2))
     return 1;
   if (!tc::make_map(&mx, g.x, (uint64_t)g.K, (uint64_t)g.M, 1, (uint64_t)g.ldx * 2, (uint64_t)g.ldx * 2 * g.M,
                     (uint32_t)p.mpad, 2))
     return 1;
   launch_pdl(e, tc::gemm_tc_swap_kernel, dim3(tiles, ksplit, row_tiles), dim3(tc::THREADS),
-             (size_t)tc::sw_smem_bytes(row_tile, bm), s, mw, mx, p);
+             (size_t)tc::sw_smem_bytes(row_tile), s, mw, mx, p);
   WDZ_LAUNCH_CHECK(e, "gemm_tc_swap");
   return WDZ_OK;
 }
@@ -793,11 +783,6 @@ int wdz_engine_create(const wdz_config* cfg, wdz_engine** out) {
   wdz_engine* e = new wdz_engine();
   e->cfg = c;
   e->esz = c.dtype == WDZ_BF16 ? 2 : 4;
-  if (const char* ks = getenv("WDZ_KSPLIT")) e->ksplit_override = atoi(ks);
-  if (const char* rt = getenv("WDZ_ROWTILE")) e->row_tile_override = atoi(rt) / 32 * 32;
-  if (const char* sq = getenv("WDZ_SPLIT_CROSS_Q")) e->split_cross_q = atoi(sq);
-  if (const char* b64 = getenv("WDZ_SW_BM64")) e->sw_bm64 = atoi(b64);
-  if (const char* gm = getenv("WDZ_GEMV_MAX_ROWS")) e->gemv_max_rows = atoi(gm);
   e->enc.resize(c.n_audio_layer);
   e->dec.resize(c.n_text_layer);
   if (cudaGetDevice(&e->device) == cudaSuccess) {
@@ -1414,10 +1399,18 @@ int wdz_ts_poll(wdz_engine* e, int32_t* out_host, wdz_stream s) {
   if (rc) return rc;
   if (!out_host) return e->fail(WDZ_EINVAL, "wdz_ts_poll: null argument");
   cudaStream_t st = (cudaStream_t)s;
+  // the status word rides along with the state download: an exhausted wait or a NaN row in any kernel since the
+  // last poll turns this call into an error without a synchronisation of its own
+  DevStatus h{};
   if (cudaMemcpyAsync(out_host, e->ts_state, sizeof(TsState) * e->cfg.n_slots, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaMemcpyAsync(&h, e->status, sizeof h, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
       cudaStreamSynchronize(st) != cudaSuccess) {
     cudaError_t ce = cudaGetLastError();
     return e->fail(WDZ_ECUDA, "rule state read: %s", cudaGetErrorString(ce));
+  }
+  if (h.code != 0) {
+    cudaMemsetAsync(e->status, 0, sizeof(DevStatus), st);
+    return e->fail(h.code, "device reported status %d (detail %d)", h.code, h.detail);
   }
   return WDZ_OK;
 }

@@ -343,7 +343,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 constexpr int SW_STAGES = 4;
 constexpr int SW_STAGE_BYTES = A_BYTES + 256 * BK * 2;   // W tile + up to 256 rows of x
 constexpr int SW_SMEM_BYTES = SW_STAGES * SW_STAGE_BYTES + 256 + 1024;   // largest launch
-inline int sw_smem_bytes(int row_tile, int bm = BM) { return SW_STAGES * (bm * BK * 2 + row_tile * BK * 2) + 256 + 1024; }
+inline int sw_smem_bytes(int row_tile) { return SW_STAGES * (A_BYTES + row_tile * BK * 2) + 256 + 1024; }
 constexpr int EPI_SW_QKV_CACHE = 16;
 
 struct TcSwapParams {
@@ -352,7 +352,6 @@ struct TcSwapParams {
   int mpad;                  // rows of one CTA's row tile, a multiple of 32 (MMA N)
   int tmem_cols;             // power of two >= mpad, >= 32
   int kb_per_split, kblocks;
-  int bm;                    // features per CTA: 128, or 64 (MMA M = 64: twice the weight streams for the same product)
   int epi;                   // EPI_STORE (f32) | EPI_GELU (bf16 out) | EPI_RESID (f32 +=) | EPI_SW_QKV_CACHE
   uint32_t idesc;
   bf16* cache_k; bf16* cache_v; const int* slots; const int* positions;
@@ -372,7 +371,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const TcSwapParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const uint32_t w_bytes = (uint32_t)p.bm * BK * 2;                   // 16 KB, or 8 KB for 64-feature tiles
+  constexpr uint32_t w_bytes = A_BYTES;                               // 128 features x 64 k, 16 KB
   const uint32_t stage_bytes = w_bytes + (uint32_t)p.mpad * BK * 2;   // a multiple of 1024
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SW_STAGES * stage_bytes);
   uint64_t* full = bars;
@@ -414,7 +413,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, p.status)) break;
         uint8_t* w_dst = smem + stage * stage_bytes;
         mbar_expect_tx(full + stage, stage_bytes);
-        tma_load_2d(w_dst, &tmW, full + stage, (kb0 + i) * BK, tile * p.bm);
+        tma_load_2d(w_dst, &tmW, full + stage, (kb0 + i) * BK, tile * BM);
         tma_load_2d(w_dst + w_bytes, &tmX, full + stage, (kb0 + i) * BK, row0);
       }
     }
@@ -441,10 +440,9 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
-      // MMA M = 128: accumulator row r sits in TMEM lane r.  M = 64: row r sits in lane 32 * (r / 16) + r % 16,
-      // so each warp's quadrant carries 16 features in its lanes 0..15 and the other lanes are idle.
-      const int n = p.bm == 128 ? tile * BM + quad * 32 + lane : tile * 64 + quad * 16 + lane;   // output feature of this thread
-      const bool n_ok = n < p.N && (p.bm == 128 || lane < 16);
+      // MMA M = 128: accumulator row r (a feature) sits in TMEM lane r
+      const int n = tile * BM + quad * 32 + lane;   // output feature of this thread
+      const bool n_ok = n < p.N;
       float bias = 0.0f;
       if (n_ok && p.bias && blockIdx.y == 0) bias = to_f(p.bias[n]);
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);

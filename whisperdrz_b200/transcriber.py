@@ -356,6 +356,7 @@ class Transcriber:
             self.steps += 1
             self.launch_rows += len(active)
             self._accept(active, nxt.tolist())
+            eng.device_status()          # a kernel that gave up (bounded wait, NaN row) must not pass for a token
         if self.aligner is not None:
             fin = [s for s in self.states if s.status == "finished"]
             if fin:
