@@ -26,6 +26,9 @@ class OracleEngine:
         self.dec = oracle.SlotDecoder(sd, dims.n_text_layer, dims.n_text_head, n_slots, dims.n_text_ctx)
         self.tables = timestamp_tables(dims.n_vocab)
 
+    def device_status(self):
+        pass
+
     def logmel(self, buf, n_samples=None, frame_offset=None):
         out = []
         for i in range(buf.shape[0]):

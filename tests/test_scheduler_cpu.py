@@ -30,6 +30,9 @@ class StubEngine:
         self.offsets = []
         self.count = {}
 
+    def device_status(self):
+        pass
+
     def logmel(self, buf, n_samples=None, frame_offset=None):
         self.calls["logmel"] += 1
         self.offsets.append(frame_offset)
