@@ -59,13 +59,23 @@ typedef struct wdz_config {
 
 /* Per-row logit rule: the device half of decode_batch
  * (src/whisperdrz/decoding.py:1514-1777).  Blocked set of a row =
- *   base(mode) | OR of tables whose bit is set in table_bits
+ *   base(mode) | OR of tables whose bit is set in table_bits | table or_table
+ *   | complement of table allow_table
  *   | ids in [prefix_begin, prefix_end) | set_ids[0..n_set)
- * with clear_ids[0..n_clear) removed last.  Blocked ids get -65504 added
- * (decoding.py:1725-1729); ids in pen_ids get the repetition penalty
- * v > 0 ? v / 1.2 : v * 1.2 (decoding.py:1733-1759); then argmax, lowest id
- * winning ties.  forced_id >= 0 skips all of that and returns forced_id
- * (rows decided on the host, decoding.py:1098-1456). */
+ * with clear_ids[0..n_clear) removed last.  This is the normal form of the
+ * reference's ordered mask steps: its "block everything, then enable a class"
+ * overrides become the base mode, its per-language base set is or_table, its
+ * tag-prefix allow list (decoding.py:1623-1639) is allow_table, its
+ * backwards-timestamp block (:1682-1689) the prefix range.
+ * Tables are bitsets over the vocabulary, bound as "rules.tables"
+ * ([n_tables][ceil(n_vocab / 32)] uint32, n_tables >= WDZ_MAX_TABLES): the first
+ * WDZ_MAX_TABLES can be OR-ed through table_bits, any table can be named by
+ * arg0 (WDZ_MODE_ALL_EXCEPT_TABLE), or_table and allow_table; there 0 means
+ * "none", so table 0 itself cannot be named by those two fields.
+ * Blocked ids get -65504 added (decoding.py:1725-1729); ids in pen_ids get the
+ * repetition penalty v > 0 ? v / 1.2 : v * 1.2 (decoding.py:1733-1759); then
+ * argmax, lowest id winning ties.  forced_id >= 0 skips all of that and returns
+ * forced_id (rows decided on the host, decoding.py:1098-1456). */
 #define WDZ_MODE_OR 0               /* base = nothing blocked */
 #define WDZ_MODE_ALL_EXCEPT_TABLE 1 /* base = everything blocked except table arg0 */
 #define WDZ_MODE_ALL_EXCEPT_RANGE 2 /* base = everything blocked except ids [arg0, arg1) */
@@ -76,7 +86,9 @@ typedef struct wdz_rule_desc {
   int32_t mode, arg0, arg1;
   uint32_t table_bits;
   int32_t prefix_begin, prefix_end;
-  int32_t n_set, set_ids[8];
+  int32_t n_set, set_ids[6];
+  int32_t or_table;    /* 0 = none, else index of one more table to OR in */
+  int32_t allow_table; /* 0 = none, else index of a table whose complement is blocked */
   int32_t n_clear, clear_ids[4];
   int32_t n_pen, pen_ids[10];
 } wdz_rule_desc; /* 32 x int32 = 128 bytes */

@@ -237,8 +237,9 @@ def blocked_mask(rule: dict, tables: torch.Tensor, V: int) -> torch.Tensor:
     """Boolean blocked-set of one row.  ``tables`` is bool [n_tables, V].
     Normal form of the ordered mask algebra of decoding.py:1527-1713: a base
     (nothing / everything except a table / everything except an id range /
-    everything), OR-ed class tables, a blocked id prefix range, single ids
-    set, then single ids cleared."""
+    everything), OR-ed class tables (the first 32 by bit, one more by index),
+    the complement of an allow-list table, a blocked id prefix range, single
+    ids set, then single ids cleared."""
     mode = rule.get("mode", MODE_OR)
     if mode == MODE_OR:
         m = torch.zeros(V, dtype=torch.bool)
@@ -250,9 +251,13 @@ def blocked_mask(rule: dict, tables: torch.Tensor, V: int) -> torch.Tensor:
     else:
         m = torch.ones(V, dtype=torch.bool)
     bits = rule.get("table_bits", 0)
-    for i in range(tables.shape[0]):
+    for i in range(min(32, tables.shape[0])):
         if bits >> i & 1:
             m |= tables[i]
+    if rule.get("or_table", 0) > 0:
+        m |= tables[rule["or_table"]]
+    if rule.get("allow_table", 0) > 0:
+        m |= ~tables[rule["allow_table"]]
     pb, pe = rule.get("prefix_begin", 0), rule.get("prefix_end", 0)
     if pe > pb:
         m[max(pb, 0): min(pe, V)] = True

@@ -13,7 +13,7 @@ def rule_from_words(w) -> dict:
     if w[0] >= 0:
         return {"forced_id": w[0]}
     return {"mode": w[1], "arg0": w[2], "arg1": w[3], "table_bits": w[4] & 0xFFFFFFFF, "prefix_begin": w[5],
-            "prefix_end": w[6], "set_ids": w[8: 8 + w[7]], "clear_ids": w[17: 17 + w[16]],
+            "prefix_end": w[6], "set_ids": w[8: 8 + w[7]], "or_table": w[14], "allow_table": w[15], "clear_ids": w[17: 17 + w[16]],
             "pen_ids": w[22: 22 + w[21]]}
 
 

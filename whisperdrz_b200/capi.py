@@ -38,7 +38,7 @@ class Config(C.Structure):
 class RuleDesc(C.Structure):
     _fields_ = [("forced_id", C.c_int32), ("mode", C.c_int32), ("arg0", C.c_int32), ("arg1", C.c_int32),
                 ("table_bits", C.c_uint32), ("prefix_begin", C.c_int32), ("prefix_end", C.c_int32),
-                ("n_set", C.c_int32), ("set_ids", C.c_int32 * 8),
+                ("n_set", C.c_int32), ("set_ids", C.c_int32 * 6), ("or_table", C.c_int32), ("allow_table", C.c_int32),
                 ("n_clear", C.c_int32), ("clear_ids", C.c_int32 * 4),
                 ("n_pen", C.c_int32), ("pen_ids", C.c_int32 * 10)]
 

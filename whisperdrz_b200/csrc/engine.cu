@@ -74,6 +74,7 @@ struct wdz_engine {
   void *self_k = nullptr, *self_v = nullptr, *cross_k = nullptr, *cross_v = nullptr;
   int* seq_lens = nullptr;
   const uint32_t* tables = nullptr;
+  int n_tables = 0;
   MelTables mel{};
 
   // workspace
@@ -595,7 +596,7 @@ int rules_launch(wdz_engine* e, const float* logits, const int* row_idx, const w
                  int penalty, int* out, cudaStream_t s) {
   if (n <= 0) return WDZ_OK;
   const int V = e->cfg.n_vocab;
-  launch_pdl(e, rules_argmax_kernel, dim3(n), dim3(1024), 0, s, logits, V, row_idx, rules, e->tables, (V + 31) / 32, V, penalty, out,
+  launch_pdl(e, rules_argmax_kernel, dim3(n), dim3(1024), 0, s, logits, V, row_idx, rules, e->tables, e->n_tables, (V + 31) / 32, V, penalty, out,
                                          e->status);
   WDZ_LAUNCH_CHECK(e, "rules_argmax");
   return WDZ_OK;
@@ -895,7 +896,22 @@ int wdz_finalize(wdz_engine* e) {
   e->cross_k = (void*)get("cache.cross_k", cross_n);
   e->cross_v = (void*)get("cache.cross_v", cross_n);
   e->seq_lens = (int*)get("cache.seq_lens", c.n_slots);
-  e->tables = (const uint32_t*)get("rules.tables", (int64_t)WDZ_MAX_TABLES * ((c.n_vocab + 31) / 32), true);
+  {
+    // class tables of the logit rules: any number of vocabulary bitsets, at least WDZ_MAX_TABLES
+    const int64_t words = (c.n_vocab + 31) / 32;
+    auto it = e->bound.find("rules.tables");
+    e->tables = nullptr; e->n_tables = 0;
+    if (it != e->bound.end()) {
+      if (it->second.numel % words || it->second.numel < (int64_t)WDZ_MAX_TABLES * words) {
+        if (rc == WDZ_OK)
+          rc = e->fail(WDZ_EINVAL, "tensor 'rules.tables' has %lld elements, expected a multiple of %lld and at least %lld",
+                       (long long)it->second.numel, (long long)words, (long long)(WDZ_MAX_TABLES * words));
+      } else {
+        e->tables = (const uint32_t*)it->second.ptr;
+        e->n_tables = (int)(it->second.numel / words);
+      }
+    }
+  }
   e->mel.twiddle = (const float2*)get("mel.twiddle", 2 * MEL_NFFT);
   e->mel.window = (const float*)get("mel.window", MEL_NFFT);
   e->mel.fb = (const float*)get("mel.fb", (int64_t)MEL_BINS * c.n_mels);

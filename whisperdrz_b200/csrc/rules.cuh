@@ -13,7 +13,7 @@ namespace wdz {
 
 __global__ void __launch_bounds__(1024)
 rules_argmax_kernel(const float* __restrict__ logits, int64_t ld, const int* __restrict__ row_idx,
-                    const wdz_rule_desc* __restrict__ rules, const uint32_t* __restrict__ tables,
+                    const wdz_rule_desc* __restrict__ rules, const uint32_t* __restrict__ tables, int n_tables,
                     int words, int V, int apply_penalty, int* __restrict__ out, DevStatus* status) {
   pdl_trigger();
   pdl_wait();
@@ -27,7 +27,7 @@ rules_argmax_kernel(const float* __restrict__ logits, int64_t ld, const int* __r
     if (rules) rd = rules[r];
     else {
       rd.forced_id = -1; rd.mode = WDZ_MODE_OR; rd.table_bits = 0; rd.prefix_begin = rd.prefix_end = 0;
-      rd.n_set = rd.n_clear = rd.n_pen = 0; rd.arg0 = rd.arg1 = 0;
+      rd.n_set = rd.n_clear = rd.n_pen = 0; rd.arg0 = rd.arg1 = 0; rd.or_table = rd.allow_table = 0;
     }
   }
   __syncthreads();
@@ -36,9 +36,15 @@ rules_argmax_kernel(const float* __restrict__ logits, int64_t ld, const int* __r
     return;
   }
   const float* lg = logits + (int64_t)(row_idx ? row_idx[r] : r) * ld;
-  const int n_set = min(max(rd.n_set, 0), 8), n_clear = min(max(rd.n_clear, 0), 4);
+  const int n_set = min(max(rd.n_set, 0), 6), n_clear = min(max(rd.n_clear, 0), 4);
   const int n_pen = apply_penalty ? min(max(rd.n_pen, 0), 10) : 0;
   const bool have_tables = tables != nullptr;
+  // tables named by index: a name outside the bound tables reads as "no table" (base table: nothing allowed)
+  const uint32_t* t_base = have_tables && rd.mode == WDZ_MODE_ALL_EXCEPT_TABLE && rd.arg0 >= 0 && rd.arg0 < n_tables
+                               ? tables + (int64_t)rd.arg0 * words : nullptr;
+  const uint32_t* t_or = have_tables && rd.or_table > 0 && rd.or_table < n_tables ? tables + (int64_t)rd.or_table * words : nullptr;
+  const uint32_t* t_allow = have_tables && rd.allow_table > 0 && rd.allow_table < n_tables
+                                ? tables + (int64_t)rd.allow_table * words : nullptr;
 
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -47,7 +53,7 @@ rules_argmax_kernel(const float* __restrict__ logits, int64_t ld, const int* __r
     bool blocked;
     if (rd.mode == WDZ_MODE_OR) blocked = false;
     else if (rd.mode == WDZ_MODE_ALL_EXCEPT_TABLE)
-      blocked = !(have_tables && ((tables[(int64_t)rd.arg0 * words + (v >> 5)] >> (v & 31)) & 1u));
+      blocked = !(t_base && ((t_base[v >> 5] >> (v & 31)) & 1u));
     else if (rd.mode == WDZ_MODE_ALL_EXCEPT_RANGE) blocked = !(v >= rd.arg0 && v < rd.arg1);
     else blocked = true;
     if (have_tables) {
@@ -58,6 +64,8 @@ rules_argmax_kernel(const float* __restrict__ logits, int64_t ld, const int* __r
         blocked |= (tables[(int64_t)t * words + (v >> 5)] >> (v & 31)) & 1u;
       }
     }
+    if (t_or) blocked |= (t_or[v >> 5] >> (v & 31)) & 1u;
+    if (t_allow) blocked |= !((t_allow[v >> 5] >> (v & 31)) & 1u);
     blocked |= (v >= rd.prefix_begin && v < rd.prefix_end);
     for (int i = 0; i < n_set; ++i) blocked |= (rd.set_ids[i] == v);
     for (int i = 0; i < n_clear; ++i) if (rd.clear_ids[i] == v) blocked = false;

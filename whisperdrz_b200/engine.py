@@ -74,7 +74,8 @@ def pack_rules(rules: list[dict]) -> np.ndarray:
         d.arg0, d.arg1 = r.get("arg0", 0), r.get("arg1", 0)
         d.table_bits = r.get("table_bits", 0)
         d.prefix_begin, d.prefix_end = r.get("prefix_begin", 0), r.get("prefix_end", 0)
-        for field, cap in (("set_ids", 8), ("clear_ids", 4), ("pen_ids", 10)):
+        d.or_table, d.allow_table = r.get("or_table", 0), r.get("allow_table", 0)
+        for field, cap in (("set_ids", 6), ("clear_ids", 4), ("pen_ids", 10)):
             ids = list(dict.fromkeys(r.get(field, [])))
             if len(ids) > cap:
                 raise ValueError(f"rule {i}: {len(ids)} {field} > {cap}")
@@ -85,13 +86,14 @@ def pack_rules(rules: list[dict]) -> np.ndarray:
 
 
 def pack_tables(tables: torch.Tensor, n_vocab: int) -> torch.Tensor:
-    """bool [n_tables <= 32, V] -> uint32 bitsets as int32 tensor [32, ceil(V / 32)]."""
+    """bool [n_tables, V] -> uint32 bitsets as int32 tensor [max(n_tables, 32), ceil(V / 32)]."""
     words = (n_vocab + 31) // 32
-    t = np.zeros((capi.MAX_TABLES, words * 32), dtype=np.uint8)
+    n = max(capi.MAX_TABLES, int(tables.shape[0]))
+    t = np.zeros((n, words * 32), dtype=np.uint8)
     tb = tables.cpu().numpy().astype(np.uint8)
     t[: tb.shape[0], :n_vocab] = tb
-    packed = np.packbits(t.reshape(capi.MAX_TABLES, words, 32), axis=-1, bitorder="little")
-    return torch.from_numpy(packed.view(np.uint32).reshape(capi.MAX_TABLES, words).view(np.int32).copy())
+    packed = np.packbits(t.reshape(n, words, 32), axis=-1, bitorder="little")
+    return torch.from_numpy(packed.view(np.uint32).reshape(n, words).view(np.int32).copy())
 
 
 class Engine:

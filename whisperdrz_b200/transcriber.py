@@ -67,7 +67,9 @@ def rules_to_array(rules: list[dict]) -> np.ndarray:
         a[i, 4] = np.int64(r.get("table_bits", 0)).astype(np.int32)
         a[i, 5] = r.get("prefix_begin", 0)
         a[i, 6] = r.get("prefix_end", 0)
-        for base, cap, key in ((7, 8, "set_ids"), (16, 4, "clear_ids"), (21, 10, "pen_ids")):
+        a[i, 14] = r.get("or_table", 0)
+        a[i, 15] = r.get("allow_table", 0)
+        for base, cap, key in ((7, 6, "set_ids"), (16, 4, "clear_ids"), (21, 10, "pen_ids")):
             ids = list(dict.fromkeys(r.get(key, ())))[:cap]
             a[i, base] = len(ids)
             a[i, base + 1: base + 1 + len(ids)] = ids
