@@ -220,6 +220,7 @@ def main():
     ap.add_argument("--clips", type=int, default=256, help="30 s chunks per GPU per step")
     ap.add_argument("--new-tokens", type=int, default=224)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cfg4", action="store_true", help="skip the 1 h strong-scaling extra (cfg4_strong_rtfx)")
     ap.add_argument("--steps-per-poll", type=int, default=8)
     ap.add_argument("--align", action="store_true",
                     help="also run the DTW word-timing alignment on every finished window (token-level words); "
@@ -318,6 +319,32 @@ def main():
     achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms > 0 else 0.0
     shares = {k: round(v["ms"], 3) for k, v in prof.items()}
 
+    # BASELINE config 4 as an extra, strong-scaling key: ONE hour of long-form audio, cut by the 30 s split into 120
+    # chunks that are sharded over the ranks, decoded and gathered on rank 0 for stitching
+    cfg4 = None
+    if not args.no_cfg4:
+        from whisperdrz_b200.sharding import transcribe_sharded
+        hour = torch.from_numpy(synth.long_form(3, 3600.0)).pin_memory()
+
+        def run_hour():
+            tr = Transcriber(eng, max_new_tokens=args.new_tokens, max_continuations=0, device_rules=True,
+                             steps_per_poll=args.steps_per_poll)
+            return transcribe_sharded(tr, hour, rank, world)
+        run_hour()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = run_hour()
+        torch.cuda.synchronize()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        eng.device_status()
+        if rank == 0:
+            cfg4 = {"cfg4_strong_rtfx": 3600.0 / float(dt.item()), "cfg4_chunks_gathered": len(res.raw_chunks),
+                    "cfg4_seconds": float(dt.item())}
+
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -332,6 +359,8 @@ def main():
                              "traffic": traffic_per_row * per_launch_bytes / (2.0 * 1500 * 1280 * 2),
                              "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms},
                 "kernel_ms_one_step": shares}
+        if cfg4:
+            line.update(cfg4)
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)

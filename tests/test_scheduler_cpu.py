@@ -318,3 +318,23 @@ def test_continuation_keeps_the_words_of_the_kept_tokens():
     assert idx == sorted(idx) and len(set(idx)) == len(idx)
     assert all(r["tokens"][i] < TOK_EOT for i in idx)            # indices point at text tokens of the stitched chunk
     assert len(idx) >= 3 and all(w[2] >= w[1] >= 0.0 for w in r["word_times"])
+
+
+def test_warm_slots_are_prefilled_in_the_background_and_promoted():
+    """n_warm extra slots (transcriber.py:559-568, 976-1040): the same chunks give the same tokens as the
+    plain scheduler, at most BS slots decode at a time, and slots enter decoding through the warm pool."""
+    audio = torch.randn(16000 * 30 * 9)
+    tp = Transcriber(StubEngine(), BS=2, max_new_tokens=12, max_continuations=0)
+    _patch_rules_dev(tp)
+    plain = tp.transcribe(audio)
+    eng = StubEngine()
+    t = Transcriber(eng, BS=2, n_warm=2, max_new_tokens=12, max_continuations=0)
+    _patch_rules_dev(t)
+    warm = t.transcribe(audio)
+    assert [r["id"] for r in warm.raw_chunks] == [r["id"] for r in plain.raw_chunks] == [f"chunk_{i}" for i in range(9)]
+    assert all(r["stop_reason"] in ("eot", "max_tokens") and r["tokens"] for r in warm.raw_chunks)
+    assert all(s.status == "ready" for s in t.states) and not t.pending_chunks
+    assert max(eng.rows_per_step) <= 2
+    assert t.promoted == 9 and not t.warming
+    with pytest.raises(ValueError):
+        Transcriber(StubEngine(), BS=4, n_warm=1)

@@ -81,7 +81,7 @@ class Transcriber:
                  max_new_tokens: int = 224, lang: str | None = "en", use_rules: bool = True,
                  text_decoder=None, max_continuations: int = 20, device_rules: bool | None = None,
                  steps_per_poll: int = 8, min_refill: int = 1, max_refill_wait: int = 4,
-                 aligner=None, align_heads=None):
+                 aligner=None, align_heads=None, n_warm: int = 0):
         """engine: ``whisperdrz_b200.engine.Engine`` (or an object with the same
         methods).  BS: concurrent slots, at most the engine's.  max_new_tokens:
         generated tokens per 30 s window before EOT is forced.  text_decoder:
@@ -96,13 +96,18 @@ class Transcriber:
         more efficient on a batch of windows), or after ``max_refill_wait``
         scheduler iterations; the reference refills one by one
         (transcriber.py:1790-1815, ``min_refill_batch = 1``), which is the default.
+        n_warm: extra slots that are prefilled in the background (transcriber.py:559-568, 976-1040): while
+        BS slots decode, up to n_warm more chunks have their log-mel, encoder and cross K/V computed on a side
+        stream; a warm slot starts decoding as soon as its event has completed and a decode slot is free,
+        paying only its prompt rows then.  BS + n_warm may not exceed the engine's slots.
         aligner: ``tokens -> [chunk dict]`` (see ``alignment.token_aligner``); when given, every finished
         window is aligned by DTW before its slot is released and results carry ``word_times``
         (the reference's ``dtw_align=True``).  align_heads: (layer, head) pairs, default the large-v3 set."""
         self.engine = engine
-        self.BS = BS or engine.n_slots
-        if self.BS > engine.n_slots:
-            raise ValueError("BS exceeds the engine's slot count")
+        self.n_warm = max(0, n_warm)
+        self.BS = BS or (engine.n_slots - self.n_warm)
+        if self.BS < 1 or self.BS + self.n_warm > engine.n_slots:
+            raise ValueError("BS + n_warm exceeds the engine's slot count")
         self.max_audio_length = max_audio_length
         self.max_new_tokens = max_new_tokens
         self.use_rules = use_rules
@@ -116,13 +121,15 @@ class Transcriber:
         self.init_tokens = [TOK_SOT, TOK_LANG_EN, TOK_TRANSCRIBE] if lang else [TOK_SOT]
         if len(self.init_tokens) + max_new_tokens > engine.max_tokens:
             raise ValueError("prompt + max_new_tokens exceed the KV cache length")
-        self.states = [Slot(i) for i in range(self.BS)]
-        self.rule_state = BatchRuleState(self.BS, max_new_tokens)
+        self.states = [Slot(i) for i in range(self.BS + self.n_warm)]
+        self.rule_state = BatchRuleState(self.BS + self.n_warm, max_new_tokens)
+        self.prefill_stream = None          # side stream of the warm slots, made on first use
+        self.warming: list = []             # [(event, [slots], xa-free marker)] prefill groups in flight
+        self.promoted = 0
         self.pending_chunks: list[dict] = []
         self.seconds_processed = 0.0
         self.steps = 0
         self.launch_rows = 0
-        self._pin_audio = None
         self.aligner = aligner
         self.windows_aligned = 0
         if aligner is not None:
@@ -181,51 +188,142 @@ class Transcriber:
     def _prefill_slots(self, slots: list[Slot]) -> None:
         """Log-mel + encoder + cross K/V + prompt for new slots, then their first token."""
         eng = self.engine
-        dev = eng.device
         for g0 in range(0, len(slots), eng.max_clips):
             grp = slots[g0: g0 + eng.max_clips]
-            n = [min(len(s.chunk["audio"]), 480000) for s in grp]
-            first = grp[0].chunk["audio"]
-            if isinstance(first, torch.Tensor) and first.is_cuda:
-                buf = torch.zeros(len(grp), 480000, dtype=torch.float32, device=dev)
-                for i, s in enumerate(grp):
-                    buf[i, : n[i]] = s.chunk["audio"][: n[i]]
-            elif dev.type == "cuda" and all(isinstance(s.chunk["audio"], torch.Tensor) and s.chunk["audio"].is_pinned()
-                                            and s.chunk["audio"].dtype == torch.float32 for s in grp):
-                # caller-pinned host audio goes to the device directly, one asynchronous copy per chunk
-                buf = torch.zeros(len(grp), 480000, dtype=torch.float32, device=dev)
-                for i, s in enumerate(grp):
-                    buf[i, : n[i]].copy_(s.chunk["audio"][: n[i]], non_blocking=True)
-            else:
-                self._pin_audio = getattr(eng, "_pin_audio", None)
-                if self._pin_audio is None:      # one pinned staging buffer per engine, reused for every group
-                    self._pin_audio = torch.zeros(eng.max_clips, 480000, dtype=torch.float32)
-                    if dev.type == "cuda":
-                        self._pin_audio = self._pin_audio.pin_memory()
-                    try:
-                        eng._pin_audio = self._pin_audio
-                    except AttributeError:
-                        pass
-                elif dev.type == "cuda":
-                    torch.cuda.current_stream(dev).synchronize()   # the previous upload has left the buffer
-                host = self._pin_audio[: len(grp)]
-                for i, s in enumerate(grp):
-                    host[i, : n[i]] = torch.as_tensor(s.chunk["audio"][: n[i]], dtype=torch.float32)
-                    host[i, n[i]:] = 0.0
-                buf = host.to(dev, non_blocking=True)
-            # a continuation window starts at its offset inside the chunk; the (max - 8) floor is still
-            # taken over the whole chunk (transcriber.py:1062-1072)
-            offs = [int(round(s.win_offset * 100)) for s in grp]
-            mel = eng.logmel(buf, n_samples=n, frame_offset=offs if any(offs) else None)
-            xa = eng.encode(mel)
-            ids = [s.index for s in grp]
+            self._first_tokens(grp, self._encode_group(grp))
+
+    def _encode_group(self, grp: list[Slot]):
+        """Audio upload, log-mel, encoder and cross K/V of at most max_clips windows, on the current stream.
+        Returns None, or the encoder states when the engine only offers the fused prefill call."""
+        eng = self.engine
+        dev = eng.device
+        n = [min(len(s.chunk["audio"]), 480000) for s in grp]
+        first = grp[0].chunk["audio"]
+        if isinstance(first, torch.Tensor) and first.is_cuda:
+            buf = torch.zeros(len(grp), 480000, dtype=torch.float32, device=dev)
+            for i, s in enumerate(grp):
+                buf[i, : n[i]] = s.chunk["audio"][: n[i]]
+        elif dev.type == "cuda" and all(isinstance(s.chunk["audio"], torch.Tensor) and s.chunk["audio"].is_pinned()
+                                        and s.chunk["audio"].dtype == torch.float32 for s in grp):
+            # caller-pinned host audio goes to the device directly, one asynchronous copy per chunk
+            buf = torch.zeros(len(grp), 480000, dtype=torch.float32, device=dev)
+            for i, s in enumerate(grp):
+                buf[i, : n[i]].copy_(s.chunk["audio"][: n[i]], non_blocking=True)
+        else:
+            host = self._staging(len(grp))
+            for i, s in enumerate(grp):
+                host[i, : n[i]] = torch.as_tensor(s.chunk["audio"][: n[i]], dtype=torch.float32)
+                host[i, n[i]:] = 0.0
+            buf = host.to(dev, non_blocking=True)
+            if dev.type == "cuda":
+                self._pin_busy[id(host)] = torch.cuda.Event()
+                self._pin_busy[id(host)].record(torch.cuda.current_stream(dev))
+        # a continuation window starts at its offset inside the chunk; the (max - 8) floor is still
+        # taken over the whole chunk (transcriber.py:1062-1072)
+        offs = [int(round(s.win_offset * 100)) for s in grp]
+        mel = eng.logmel(buf, n_samples=n, frame_offset=offs if any(offs) else None)
+        xa = eng.encode(mel)
+        if hasattr(eng, "cross_kv") and hasattr(eng, "forward_rows"):
+            eng.cross_kv(xa, [s.index for s in grp])
+            return None
+        return xa
+
+    def _staging(self, rows: int) -> torch.Tensor:
+        """A pinned host buffer for one group of windows whose previous upload has left it (two rotate, so that a
+        side-stream upload in flight never makes the host wait on the decode stream)."""
+        eng = self.engine
+        pool = getattr(eng, "_pin_pool", None)
+        if pool is None:
+            pool = [torch.zeros(eng.max_clips, 480000, dtype=torch.float32) for _ in range(2)]
+            if eng.device.type == "cuda":
+                pool = [b.pin_memory() for b in pool]
+            try:
+                eng._pin_pool = pool
+            except AttributeError:
+                pass
+            self._pin_busy, self._pin_next = {}, 0
+        if not hasattr(self, "_pin_busy"):
+            self._pin_busy, self._pin_next = {}, 0
+        buf = pool[self._pin_next % len(pool)]
+        self._pin_next += 1
+        ev = self._pin_busy.pop(id(buf), None)
+        if ev is not None:
+            ev.synchronize()
+        return buf[:rows]
+
+    def _first_tokens(self, grp: list[Slot], xa=None) -> None:
+        """Prompt rows of slots whose cross K/V are in place (or come with ``xa``), and their first token, on
+        the current stream."""
+        eng = self.engine
+        ids = [s.index for s in grp]
+        if xa is not None:
             logits = eng.prefill(xa, ids, [self.init_tokens] * len(grp))
-            if self.device_rules:
-                eng.ts_reset(ids, [self.max_new_tokens] * len(ids))
-                eng.ts_first(logits, ids)
+        else:
+            P = len(self.init_tokens)
+            eng.slot_reset(ids)
+            logits = eng.forward_rows(self.init_tokens * len(grp), [i for i in ids for _ in range(P)],
+                                      list(range(P)) * len(grp), emit_rows=list(range(P - 1, P * len(grp), P)))
+        if self.device_rules:
+            eng.ts_reset(ids, [self.max_new_tokens] * len(ids))
+            eng.ts_first(logits, ids)
+        else:
+            rules = self._rules_dev(self.rule_state.rules_array(ids)) if self.use_rules else None
+            self._accept(grp, eng.rules_argmax(logits, rules).tolist())
+
+    # ---- warm slots: prefill on a side stream (transcriber.py:976-1040)
+    def _kick_off_async_prefill(self, grp: list[Slot]) -> None:
+        dev = self.engine.device
+        for s in grp:
+            s.status = "warming"
+        if dev.type != "cuda":
+            self.warming.append((None, grp, self._encode_group(grp)))
+            return
+        if self.prefill_stream is None:
+            self.prefill_stream = torch.cuda.Stream(dev)
+        main = torch.cuda.current_stream(dev)
+        self.prefill_stream.wait_stream(main)      # the slots' previous windows have been read (alignment)
+        with torch.cuda.stream(self.prefill_stream):
+            xa = self._encode_group(grp)
+            ev = torch.cuda.Event()
+            ev.record(self.prefill_stream)
+        self.warming.append((ev, grp, xa))
+
+    def _promote_warm_slots(self, room: int, must: bool) -> list[Slot]:
+        """Starts decoding for warm slots whose prefill event has completed, oldest first, as far as ``room``
+        decode slots are free.  ``must``: nothing else is decoding, so wait for the oldest group."""
+        out: list[Slot] = []
+        while self.warming and room > 0:
+            ev, grp, xa = self.warming[0]
+            if ev is not None:
+                if not ev.query() and not (must and not out):
+                    break
+                torch.cuda.current_stream(self.engine.device).wait_event(ev)
+            k = min(room, len(grp))
+            now, rest = grp[:k], grp[k:]
+            if rest:
+                self.warming[0] = (ev, rest, None if xa is None else xa[k:])
             else:
-                rules = self._rules_dev(self.rule_state.rules_array(ids)) if self.use_rules else None
-                self._accept(grp, eng.rules_argmax(logits, rules).tolist())
+                self.warming.pop(0)
+            for s in now:
+                s.status = "started"
+            self._first_tokens(now, None if xa is None else xa[:k])
+            room -= k
+            out += now
+            self.promoted += k
+        return out
+
+    def _fill_warm_slots(self) -> None:
+        eng = self.engine
+        while self.pending_chunks:
+            n_warming = sum(len(g) for _, g, _ in self.warming)
+            free = [s for s in self.states if s.status == "ready"]
+            take = min(self.n_warm - n_warming, len(free), len(self.pending_chunks), eng.max_clips)
+            if take <= 0:
+                break
+            grp = free[:take]
+            for s in grp:
+                self._init_slot(s, self.pending_chunks.pop(0))
+            self._kick_off_async_prefill(grp)
 
     def _rules_dev(self, rules) -> torch.Tensor:
         """int32 [n, 32] descriptor array (or a list of rule dicts) -> device tensor."""
@@ -318,22 +416,35 @@ class Transcriber:
         done: list[dict] = []
         new = []
         cont = [s for s in self.states if s.status == "continue"]
-        free = [s for s in self.states if s.status == "ready"]
-        busy = any(s.status == "started" for s in self.states)
-        n_admit = min(len(free), len(self.pending_chunks))
-        if n_admit and busy and len(cont) + n_admit < self.min_refill and self._refill_waited < self.max_refill_wait:
-            self._refill_waited += 1          # let a larger prefill batch build up while the others decode
-            n_admit, cont = 0, []
+        if self.n_warm > 0:
+            # continuation windows are prefilled in place; new chunks only enter through the warm pool
+            for s in cont:
+                s.status = "started"
+            if cont:
+                self._prefill_slots(cont)
+            started = sum(1 for s in self.states if s.status == "started")
+            self._promote_warm_slots(self.BS - started, must=started == 0)
+            self._fill_warm_slots()
+            started = sum(1 for s in self.states if s.status == "started")
+            if started == 0 and self.warming:
+                self._promote_warm_slots(self.BS, must=True)
         else:
-            self._refill_waited = 0
-        for s in cont:
-            s.status = "started"
-            new.append(s)
-        for s in free[:n_admit]:
-            self._init_slot(s, self.pending_chunks.pop(0))
-            new.append(s)
-        if new:
-            self._prefill_slots(new)
+            free = [s for s in self.states if s.status == "ready"]
+            busy = any(s.status == "started" for s in self.states)
+            n_admit = min(len(free), len(self.pending_chunks))
+            if n_admit and busy and len(cont) + n_admit < self.min_refill and self._refill_waited < self.max_refill_wait:
+                self._refill_waited += 1          # let a larger prefill batch build up while the others decode
+                n_admit, cont = 0, []
+            else:
+                self._refill_waited = 0
+            for s in cont:
+                s.status = "started"
+                new.append(s)
+            for s in free[:n_admit]:
+                self._init_slot(s, self.pending_chunks.pop(0))
+                new.append(s)
+            if new:
+                self._prefill_slots(new)
         active = [s for s in self.states if s.status == "started"]
         if active and self.device_rules:
             # several steps per host round trip: rules, argmax and state updates all stay on the GPU
@@ -362,7 +473,13 @@ class Transcriber:
         if self.aligner is not None:
             fin = [s for s in self.states if s.status == "finished"]
             if fin:
+                # the alignment pass borrows the encoder's activation workspace: keep it apart from a
+                # warm-slot encoder run on the side stream
+                if self.prefill_stream is not None:
+                    torch.cuda.current_stream(eng.device).wait_stream(self.prefill_stream)
                 self._align_finished(fin)
+                if self.prefill_stream is not None:
+                    self.prefill_stream.wait_stream(torch.cuda.current_stream(eng.device))
         for s in self.states:
             if s.status == "finished":
                 r = self._finish(s)
