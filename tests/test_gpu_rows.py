@@ -91,7 +91,7 @@ def test_large_v3_bf16_ragged_rows_32_and_256(large, golden):
     g, prompts = golden
     stride = int(g["stride"])
     steps = g["tokens"].shape[1] - 1
-    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=N_ROWS * 9, max_clips=8, max_rows=1280,
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=N_ROWS * 9, max_clips=8, max_rows=2048,
                tables=timestamp_tables(dims.n_vocab))
     logits0 = _prefill(e, dims, prompts)
     worst = _worst(logits0, g, 0, stride)
@@ -161,7 +161,7 @@ def test_large_v3_fp32_ragged_rows_tokens_identical(large, golden):
     g, prompts = golden
     stride = int(g["stride"])
     steps = g["tokens"].shape[1] - 1
-    e = Engine(dims, sd, dtype=torch.float32, n_slots=N_ROWS, max_clips=8, max_rows=1280)
+    e = Engine(dims, sd, dtype=torch.float32, n_slots=N_ROWS, max_clips=8, max_rows=2048)
     logits = _prefill(e, dims, prompts)
     rule = [{"set_ids": [TOK_EOT]}] * N_ROWS
     cur = e.rules_argmax(logits, rule)
