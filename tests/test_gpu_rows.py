@@ -5,9 +5,15 @@ with prompts of 4..420 tokens, 24 teacher-forced decode steps.
 This is the configuration the throughput benchmark and the 32-slot decode case
 run: more than 16 rows per step take the operand-swapped tcgen05 products with
 K splits, the split cross-attention query product, the multi-way split
-cross-attention and the captured step graph.  Tolerances as everywhere: bf16
-teacher-forced logits within 3e-2 x the row's logit RMS (max-abs), fp32 greedy
-token ids identical."""
+cross-attention and the captured step graph.
+
+Tolerances.  fp32: greedy token ids identical, logits within 1e-3 x RMS.
+bf16: every comparison here takes the maximum over 32 rows x 535 logits, and at
+that sample size rounding the WEIGHTS to bf16 alone - all arithmetic in fp32,
+measured below with the fp32 engine as a control - already gives a max-abs of
+3.1-3.3e-2 x the row's logit RMS (RMS error 0.80e-2).  So the bound is stated as:
+99.9 % of the logits within 3e-2 x RMS, none beyond 5e-2, RMS error at most
+1.1e-2, and the engine's RMS error at most 1.25 x the control's."""
 import os
 
 import numpy as np
@@ -20,7 +26,9 @@ from whisperdrz_b200.weights import init_state_dict
 
 pytestmark = pytest.mark.gpu
 
-BF16_LOGIT_TOL = 3e-2
+BF16_LOGIT_TOL = 3e-2          # 99.9 % of the logits
+BF16_LOGIT_CAP = 5e-2          # every logit
+BF16_RMS_TOL = 1.1e-2
 N_ROWS = 32
 
 
@@ -64,14 +72,26 @@ def _prefill(e, dims, prompts, slot0: int = 0):
     return torch.cat(out)
 
 
-def _worst(logits, g, step, stride):
-    """max over rows of max-abs(logits - recorded) / recorded row RMS; row r is compared with recorded row r % 32."""
+def _errors(logits, g, step, stride):
+    """|logits - recorded| / recorded row RMS, [replicas, 32, 535]; row r is compared with recorded row r % 32."""
     ref = torch.from_numpy(g["logits"][:, step])
     rms = torch.from_numpy(g["rms"][:, step]).float()
     got = logits[:, ::stride].float().cpu()
     reps = got.shape[0] // N_ROWS
-    err = (got.view(reps, N_ROWS, -1) - ref[None]).abs().amax(-1) / rms[None]
-    return float(err.max())
+    return (got.view(reps, N_ROWS, -1) - ref[None]).abs() / rms[None, :, None]
+
+
+def _worst(logits, g, step, stride):
+    return float(_errors(logits, g, step, stride).max())
+
+
+def _check_bf16(logits, g, step, stride, what):
+    err = _errors(logits, g, step, stride)
+    assert float(err.max()) < BF16_LOGIT_CAP, (what, step, float(err.max()))
+    assert float((err < BF16_LOGIT_TOL).float().mean()) >= 0.999, (what, step)
+    rms = float(err.pow(2).mean().sqrt())
+    assert rms < BF16_RMS_TOL, (what, step, rms)
+    return rms
 
 
 def _replicate(e, prompts, n_copies):
@@ -94,8 +114,7 @@ def test_large_v3_bf16_ragged_rows_32_and_256(large, golden):
     e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=N_ROWS * 9, max_clips=8, max_rows=2048,
                tables=timestamp_tables(dims.n_vocab))
     logits0 = _prefill(e, dims, prompts)
-    worst = _worst(logits0, g, 0, stride)
-    assert worst < BF16_LOGIT_TOL, ("prefill", worst)
+    rms_err = [_check_bf16(logits0, g, 0, stride, "prefill")]
     assert e.seq_lens()[:N_ROWS] == [len(p) for p in prompts]
     _replicate(e, prompts, 8)
     fed = torch.from_numpy(g["tokens"])
@@ -103,10 +122,9 @@ def test_large_v3_bf16_ragged_rows_32_and_256(large, golden):
     slots256 = list(range(N_ROWS, N_ROWS * 9))
     for step in range(steps):
         _, lg = e.decode_step(fed[:, step], slots32, want_logits=True)
-        worst = max(worst, _worst(lg, g, step + 1, stride))
+        rms_err.append(_check_bf16(lg, g, step + 1, stride, "32 rows"))
         _, lg = e.decode_step(fed[:, step].repeat(8), slots256, want_logits=True)
-        worst = max(worst, _worst(lg, g, step + 1, stride))
-        assert worst < BF16_LOGIT_TOL, (step, worst)
+        _check_bf16(lg, g, step + 1, stride, "256 rows")
     e.device_status()
     lens = e.seq_lens()
     assert lens[:N_ROWS] == [len(p) + steps for p in prompts]
@@ -151,6 +169,19 @@ def test_large_v3_bf16_ragged_rows_32_and_256(large, golden):
     assert [a[s] for s in slots256[:N_ROWS]] == [a[s] for s in slots256[N_ROWS: 2 * N_ROWS]]   # replicas decode alike
     e.device_status()
     e.close()
+    del e
+    torch.cuda.empty_cache()
+
+    # control: the same weights rounded to bf16, every operation in fp32 (the fp32 engine)
+    c = Engine(dims, {k: v.bfloat16().float() for k, v in sd.items()}, dtype=torch.float32, n_slots=N_ROWS,
+               max_clips=8, max_rows=2048)
+    lg = _prefill(c, dims, prompts)
+    floor = [float(_errors(lg, g, 0, stride).pow(2).mean().sqrt())]
+    for step in range(6):
+        _, lg = c.decode_step(fed[:, step], slots32, want_logits=True)
+        floor.append(float(_errors(lg, g, step + 1, stride).pow(2).mean().sqrt()))
+    c.close()
+    assert np.mean(rms_err[: len(floor)]) <= 1.25 * np.mean(floor), (rms_err[: len(floor)], floor)
 
 
 def test_large_v3_fp32_ragged_rows_tokens_identical(large, golden):
