@@ -217,7 +217,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--model", default="large-v3")
-    ap.add_argument("--clips", type=int, default=256, help="30 s chunks per GPU per step")
+    ap.add_argument("--clips", type=int, default=384,
+                    help="30 s chunks per GPU per step = decode rows per step (384 slots hold 122 GB of KV cache)")
     ap.add_argument("--new-tokens", type=int, default=224)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cfg4", action="store_true", help="skip the 1 h strong-scaling extra (cfg4_strong_rtfx)")

@@ -150,6 +150,7 @@ namespace {
   } while (0)
 
 size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+constexpr int SW_MAX_ROWS = 512;   // token rows per launch of the operand-swapped decode product
 
 // Launch with the programmatic stream-serialization attribute (kernels that call pdl_wait()).
 template <typename... KArgs, typename... Args>
@@ -433,10 +434,10 @@ int launch_gemv_mma(wdz_engine* e, const GemvMmaParams& p, cudaStream_t s) {
   int rc = 1;
 #ifdef WDZ_WITH_TC
   if (p.M > e->gemv_max_rows && !(e->cfg.flags & WDZ_FLAG_NO_TENSOR_CORE)) {
-    // the operand-swapped tcgen05 kernel takes up to 256 rows per launch
-    for (int m0 = 0; m0 < p.M; m0 += 256) {
+    // the operand-swapped tcgen05 kernel takes up to SW_MAX_ROWS rows per launch, in row tiles of at most 256
+    for (int m0 = 0; m0 < p.M; m0 += SW_MAX_ROWS) {
       GemvMmaParams q = p;
-      q.M = p.M - m0 < 256 ? p.M - m0 : 256;
+      q.M = p.M - m0 < SW_MAX_ROWS ? p.M - m0 : SW_MAX_ROWS;
       q.x = p.x + (int64_t)m0 * p.ldx;
       q.y = OUT_BF16 ? (void*)((bf16*)p.y + (int64_t)m0 * p.ldy) : (void*)((float*)p.y + (int64_t)m0 * p.ldy);
       if (p.slots) q.slots = p.slots + m0;
@@ -686,7 +687,7 @@ static int attn_tc_chunks_launch(wdz_engine* e, const void* q, void* out, const 
 // Decode-shaped product through the operand-swapped tcgen05 kernel.  Returns 1
 // when the shape is left to the mma.sync kernel.
 static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, cudaStream_t s) {
-  if (g.M < 1 || g.M > 256 || g.K % tc::BK) return 1;
+  if (g.M < 1 || g.M > SW_MAX_ROWS || g.K % tc::BK) return 1;
   if ((((uintptr_t)g.x | (uintptr_t)g.W) & 15) || (g.ldx * 2) % 16) return 1;
   tc::TcSwapParams p{};
   p.bias = g.bias; p.y = g.y; p.ldy = g.ldy; p.M = g.M; p.N = g.N; p.K = g.K;
@@ -705,6 +706,7 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
     for (int rt = 32; rt < mpad_all; rt *= 2)
       if (tiles * ((g.M + rt - 1) / rt) <= e->sm_count) { row_tile = rt; break; }
   }
+  if (row_tile > 256) row_tile = 256;   // a row tile is the MMA N dimension and one accumulator of TMEM columns
   p.mpad = row_tile;
   const int row_tiles = (g.M + row_tile - 1) / row_tile;
   p.tmem_cols = 32;
