@@ -2,8 +2,8 @@
 reference's own recording (tests/golden/make_golden.py --large-rows): 32 slots
 with prompts of 4..420 tokens, 24 teacher-forced decode steps.
 
-This is the configuration the throughput benchmark and the 32-slot decode case
-run: more than 16 rows per step take the operand-swapped tcgen05 products with
+These are the configurations the throughput benchmark (384 rows per step) and
+the 32-slot decode case run: more than 16 rows per step take the operand-swapped tcgen05 products with
 K splits, the split cross-attention query product, the multi-way split
 cross-attention and the captured step graph.
 
@@ -30,6 +30,7 @@ BF16_LOGIT_TOL = 3e-2          # 99.8 % of the logits
 BF16_LOGIT_CAP = 5e-2          # every logit
 BF16_RMS_TOL = 1.1e-2
 N_ROWS = 32
+REPLICAS = 12                  # 384 rows per step, what the throughput benchmark batches per GPU
 
 
 def rows_inputs(n_rows: int = N_ROWS, seed: int = 2):
@@ -103,49 +104,49 @@ def _replicate(e, prompts, n_copies):
         e.seq_lens_dev[lo: lo + N_ROWS] = e.seq_lens_dev[:N_ROWS]
 
 
-def test_large_v3_bf16_ragged_rows_32_and_256(large, golden):
-    """(1) 32 ragged rows per step and (2) 256 rows per step (the 32 recorded slots replicated eight times:
+def test_large_v3_bf16_ragged_rows_32_and_384(large, golden):
+    """(1) 32 ragged rows per step and (2) 384 rows per step (the 32 recorded slots replicated twelve times:
     every replica must reproduce its recorded row) through wdz_prefill + the wdz_decode_step graph."""
     from whisperdrz_b200.engine import Engine
     dims, sd = large
     g, prompts = golden
     stride = int(g["stride"])
     steps = g["tokens"].shape[1] - 1
-    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=N_ROWS * 9, max_clips=8, max_rows=2048,
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=N_ROWS * (1 + REPLICAS), max_clips=8, max_rows=2048,
                tables=timestamp_tables(dims.n_vocab))
     logits0 = _prefill(e, dims, prompts)
     rms_err = [_check_bf16(logits0, g, 0, stride, "prefill")]
     assert e.seq_lens()[:N_ROWS] == [len(p) for p in prompts]
-    _replicate(e, prompts, 8)
+    _replicate(e, prompts, REPLICAS)
     fed = torch.from_numpy(g["tokens"])
     slots32 = list(range(N_ROWS))
-    slots256 = list(range(N_ROWS, N_ROWS * 9))
+    slots_big = list(range(N_ROWS, N_ROWS * (1 + REPLICAS)))
     for step in range(steps):
         _, lg = e.decode_step(fed[:, step], slots32, want_logits=True)
         rms_err.append(_check_bf16(lg, g, step + 1, stride, "32 rows"))
-        _, lg = e.decode_step(fed[:, step].repeat(8), slots256, want_logits=True)
-        _check_bf16(lg, g, step + 1, stride, "256 rows")
+        _, lg = e.decode_step(fed[:, step].repeat(REPLICAS), slots_big, want_logits=True)
+        _check_bf16(lg, g, step + 1, stride, "384 rows")
     e.device_status()
     lens = e.seq_lens()
     assert lens[:N_ROWS] == [len(p) + steps for p in prompts]
-    assert lens[N_ROWS:] == lens[:N_ROWS] * 8
+    assert lens[N_ROWS:] == lens[:N_ROWS] * REPLICAS
 
     # (3) rule state kept on the device (wdz_ts_first / wdz_ts_steps, several steps per host round trip) at
-    # 256 rows against the same engine stepped from the host with the same token-level rules: rewind the
+    # 384 rows against the same engine stepped from the host with the same token-level rules: rewind the
     # slots to their prompts and decode 8 tokens each way.  The bf16 step is not bit-reproducible (K-split
     # partial sums meet in fp32 atomics, and a last-bit difference can flip a bf16 rounding further down),
     # so a free-running row now and then takes another of two near-equal logits - replicas of one row do
     # that within a single run, too.  Required: the first two tokens of every row agree and at least 80 % of
     # the rows agree on all eight (a wrong slot, position or rule on either path would leave none).
     n_new = 8
-    lens0 = torch.tensor([len(p) for p in prompts] * 9, dtype=torch.int32).cuda()
-    first = logits0.repeat(8, 1)
+    lens0 = torch.tensor([len(p) for p in prompts] * (1 + REPLICAS), dtype=torch.int32).cuda()
+    first = logits0.repeat(REPLICAS, 1)
 
     def host_path():
         e.seq_lens_dev.copy_(lens0)
-        rs = BatchRuleState(N_ROWS * 9, n_new)
-        toks = {s: [] for s in slots256}
-        active = list(slots256)
+        rs = BatchRuleState(N_ROWS * (1 + REPLICAS), n_new)
+        toks = {s: [] for s in slots_big}
+        active = list(slots_big)
         cur = e.rules_argmax(first, torch.from_numpy(rs.rules_array(np.asarray(active))).cuda()).tolist()
         for i in range(n_new):
             done = rs.update(np.asarray(active), cur)
@@ -160,17 +161,17 @@ def test_large_v3_bf16_ragged_rows_32_and_256(large, golden):
 
     def device_path():
         e.seq_lens_dev.copy_(lens0)
-        e.ts_reset(slots256, [n_new] * len(slots256))
-        e.ts_first(first, slots256)
-        e.ts_steps(slots256, 3)
-        e.ts_steps(slots256, n_new - 3 - 1)
+        e.ts_reset(slots_big, [n_new] * len(slots_big))
+        e.ts_first(first, slots_big)
+        e.ts_steps(slots_big, 3)
+        e.ts_steps(slots_big, n_new - 3 - 1)
         st = e.ts_poll()
-        return {s: e.ts_tokens(s, int(st[s][1])) for s in slots256}
+        return {s: e.ts_tokens(s, int(st[s][1])) for s in slots_big}
 
     a, b = host_path(), device_path()
-    assert all(a[s][:2] == b[s][:2] for s in slots256)
-    assert sum(a[s] == b[s] for s in slots256) >= 0.8 * len(slots256)
-    assert all(len(b[s]) == n_new or b[s][-1] == TOK_EOT for s in slots256)
+    assert all(a[s][:2] == b[s][:2] for s in slots_big)
+    assert sum(a[s] == b[s] for s in slots_big) >= 0.8 * len(slots_big)
+    assert all(len(b[s]) == n_new or b[s][-1] == TOK_EOT for s in slots_big)
     e.device_status()
     e.close()
     del e
