@@ -133,6 +133,8 @@ struct AttnDecParams {
   int chunk, max_splits;
   float* part_o; float* part_ml;    // [rows, max_splits, H, 64] and [rows, max_splits, H, 2]
   void* out; int64_t ldo;           // combine: out (TO) + r * ldo + h * 64
+  int* counters;                    // [rows], zero between launches: split CTAs of a row count themselves in, the
+                                    // last one merges the row's partial results (nullptr: a combine launch follows)
 };
 
 // Block = a group of heads (warp = head); grid = (splits, rows, head groups).
@@ -265,6 +267,9 @@ __device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity, vo
   }
 }
 
+template <typename TO>
+__device__ __forceinline__ void attn_dec_merge_head(const AttnDecParams& p, int r, int h, int lane, int H, int nsplit);
+
 template <typename T>
 __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p, DevStatus* status) {
   constexpr int VEC = Vec<T>::N;
@@ -375,7 +380,7 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
       m = m_new;
     }
   }
-  if (!ok) return;
+  if (!ok && !p.counters) return;
 #pragma unroll
   for (int o2 = LPK; o2 < 32; o2 <<= 1) {
     const float m2 = __shfl_xor_sync(0xffffffffu, m, o2);
@@ -397,6 +402,23 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
     for (int e = 0; e < VEC; ++e) p.part_o[pi * HD + piece * VEC + e] = o[e];
   }
   if (lane == 0) { p.part_ml[pi * 2] = m; p.part_ml[pi * 2 + 1] = l; }
+  if (!p.counters) return;
+  // The split CTAs of a row count themselves in; whichever comes last finds all partial results in place and
+  // merges them, so no combine launch is needed and nobody waits for anybody.  (After an exhausted wait the
+  // CTA still counts itself in: the status word already tells the host that the output is void.)
+  __shared__ int s_last;
+  __threadfence();
+  asm volatile("bar.sync 1, %0;" ::"r"(H * 32) : "memory");          // the H head warps; the producer warp has left
+  if (threadIdx.x == 0) {
+    const int nsplit = (len + p.chunk - 1) / p.chunk;
+    const int old = atomicAdd(p.counters + r, 1);
+    s_last = old == nsplit - 1;
+    if (s_last) p.counters[r] = 0;                                   // ready for the next launch
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(H * 32) : "memory");
+  if (!s_last) return;
+  __threadfence();
+  attn_dec_merge_head<T>(p, r, h, lane, H, (len + p.chunk - 1) / p.chunk);
 }
 
 template <typename T>
@@ -404,18 +426,10 @@ inline size_t attn_dec_stream_smem(int d) {
   return (size_t)ATT_STAGES * 2 * (2 * (32 / (HD / Vec<T>::N))) * d * sizeof(T) + 2 * ATT_STAGES * 8 + 16;
 }
 
-// Block = H warps; grid = rows.  Merges the splits that the row's length makes valid.
+// Merges the nsplit partial results of (row r, head h) and writes the normalised output; one warp per head.
+// Partials written by other CTAs are read past L1 (ld.global.cg).
 template <typename TO>
-__global__ void attn_dec_combine_kernel(AttnDecParams p) {
-  pdl_trigger();
-  pdl_wait();
-  const int r = blockIdx.x;
-  const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, H = blockDim.x >> 5;
-  const int slot = p.slots[r];
-  if (slot < 0 || slot >= p.n_slots) return;
-  int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
-  len = len > p.S ? p.S : len;
-  const int nsplit = (len + p.chunk - 1) / p.chunk;
+__device__ __forceinline__ void attn_dec_merge_head(const AttnDecParams& p, int r, int h, int lane, int H, int nsplit) {
   const int64_t base = (int64_t)r * p.max_splits * H + h;   // entry of split s: base + s * H
   float o0 = 0.0f, o1 = 0.0f, L = 0.0f, M = -INFINITY;
   // splits in groups of 32: lanes fetch (m, l) of different splits in parallel
@@ -423,7 +437,7 @@ __global__ void attn_dec_combine_kernel(AttnDecParams p) {
     const int s = s0 + lane;
     float ms = -INFINITY, ls = 0.0f;
     if (s < nsplit) {
-      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + (base + (int64_t)s * H) * 2);
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (base + (int64_t)s * H) * 2));
       ms = ml.x; ls = ml.y;
     }
     const float M_new = fmaxf(M, warp_max(ms));
@@ -439,8 +453,8 @@ __global__ void attn_dec_combine_kernel(AttnDecParams p) {
       for (int u = 0; u < 16; ++u) {
         const bool ok = i0 + u < cnt;
         const float* po = p.part_o + (base + (int64_t)(s0 + (ok ? i0 + u : 0)) * H) * HD;
-        x0[u] = ok ? po[lane] : 0.0f;
-        x1[u] = ok ? po[32 + lane] : 0.0f;
+        x0[u] = ok ? __ldcg(po + lane) : 0.0f;
+        x1[u] = ok ? __ldcg(po + 32 + lane) : 0.0f;
       }
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
@@ -455,6 +469,20 @@ __global__ void attn_dec_combine_kernel(AttnDecParams p) {
   TO* dst = reinterpret_cast<TO*>(p.out) + (int64_t)r * p.ldo + h * HD;
   dst[lane] = from_f<TO>(o0 * inv);
   dst[32 + lane] = from_f<TO>(o1 * inv);
+}
+
+// Block = H warps; grid = rows.  Merges the splits that the row's length makes valid.
+template <typename TO>
+__global__ void attn_dec_combine_kernel(AttnDecParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, H = blockDim.x >> 5;
+  const int slot = p.slots[r];
+  if (slot < 0 || slot >= p.n_slots) return;
+  int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
+  len = len > p.S ? p.S : len;
+  attn_dec_merge_head<TO>(p, r, h, lane, H, (len + p.chunk - 1) / p.chunk);
 }
 
 }  // namespace wdz

@@ -85,6 +85,7 @@ struct wdz_engine {
   float* x = nullptr;
   float *dx = nullptr, *dxn = nullptr, *dqkv = nullptr, *dao = nullptr, *dq = nullptr, *dh = nullptr;
   float *part_o = nullptr, *part_ml = nullptr, *logits = nullptr;
+  int* att_counters = nullptr;   // [max_rows] arrival counters of the split decode attention, zero between launches
   int* dpos = nullptr;
   int* al_slots = nullptr;     // rows of a teacher-forced alignment pass
   int* al_pos = nullptr;
@@ -211,6 +212,7 @@ size_t carve(wdz_engine* e, char* base) {
   e->part_entries = part_entries_for(c);
   e->part_o = (float*)take(sizeof(float) * e->part_entries * H * HD);
   e->part_ml = (float*)take(sizeof(float) * e->part_entries * H * 2);
+  e->att_counters = (int*)take(sizeof(int) * R);
   e->max_emit = c.max_rows < c.n_slots ? c.max_rows : c.n_slots;
   if (e->max_emit < 1) e->max_emit = 1;
   e->logits = (float*)take(sizeof(float) * (int64_t)e->max_emit * c.n_vocab);
@@ -414,7 +416,11 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
   const int sp = e->span_begin(cross ? WDZ_PROF_CROSS_ATTN : WDZ_PROF_SELF_ATTN,
                                cross ? 2.0 * rows * max_len * p.d * sizeof(T) : 0.0, s);
   if (stream) {
+    p.counters = e->att_counters;   // the last split CTA of a row merges the row: no combine launch
     launch_pdl(e, attn_dec_stream_kernel<T>, dim3(splits, rows), dim3((H + 1) * 32), attn_dec_stream_smem<T>(p.d), s, p, e->status);
+    e->span_end(sp, s);
+    WDZ_LAUNCH_CHECK(e, "attn_dec_stream");
+    return WDZ_OK;
   } else {
     int hpc = 1;  // heads per CTA: the largest divisor of H up to 5, so that several CTAs share an SM
     for (int c = 2; c <= 5; ++c) if (H % c == 0) hpc = c;
@@ -830,7 +836,8 @@ int wdz_set_workspace(wdz_engine* e, void* dev, size_t bytes) {
   carve(e, base);
   e->ws = base;
   e->ws_bytes = bytes;
-  if (cudaMemset(e->status, 0, sizeof(DevStatus)) != cudaSuccess) {
+  if (cudaMemset(e->status, 0, sizeof(DevStatus)) != cudaSuccess ||
+      cudaMemset(e->att_counters, 0, sizeof(int) * e->cfg.max_rows) != cudaSuccess) {
     cudaGetLastError();
     return e->fail(WDZ_ECUDA, "cannot clear the status word");
   }
@@ -972,6 +979,7 @@ int wdz_device_status(wdz_engine* e, wdz_stream s) {
   }
   if (h.code != 0) {
     cudaMemsetAsync(e->status, 0, sizeof(DevStatus), st);
+    cudaMemsetAsync(e->att_counters, 0, sizeof(int) * e->cfg.max_rows, st);   // a kernel that gave up may have left counts behind
     return e->fail(h.code, "device reported status %d (detail %d)", h.code, h.detail);
   }
   return WDZ_OK;
