@@ -219,6 +219,7 @@ def main():
     ap.add_argument("--model", default="large-v3")
     ap.add_argument("--clips", type=int, default=384,
                     help="30 s chunks per GPU per step = decode rows per step (384 slots hold 122 GB of KV cache)")
+    ap.add_argument("--max-clips", type=int, default=32, help="windows per encoder call (32: fuller tile waves than 16)")
     ap.add_argument("--new-tokens", type=int, default=224)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cfg4", action="store_true", help="skip the 1 h strong-scaling extra (cfg4_strong_rtfx)")
@@ -249,7 +250,7 @@ def main():
 
     dims = ModelDimensions.from_name(args.model)
     sd = init_state_dict(dims, 0)
-    eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(16, args.clips),
+    eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(args.max_clips, args.clips),
                  max_rows=max(args.clips, 64, 4096 if args.align else 0),
                  tables=timestamp_tables(dims.n_vocab))
     audio_host = torch.from_numpy(synth.clips([1000 * rank + i + 1 for i in range(args.clips)])).pin_memory()
