@@ -108,29 +108,25 @@ def cfg3(dims, sd):
     p_len, g_len, prompts = synth.decode_lengths(2, B, dims.n_text_ctx)
 
     def run():
-        tr = Transcriber(e, max_new_tokens=1)   # only its rule state and bookkeeping are used
-        rs = tr.rule_state
+        # rule state on the device: eight decode steps per host round trip, rows that reach their drawn length are
+        # forced to EOS and dropped there; the host only re-stages the list of live slots between polls
         e.slot_reset(range(B))
         tok, sl, pos, emit = [], [], [], []
         for b in range(B):
-            rs.reset(b, int(g_len[b]))
             for j, t in enumerate(prompts[b]):
                 tok.append(int(t)); sl.append(b); pos.append(j)
             emit.append(len(tok) - 1)
         logits = e.forward_rows(tok, sl, pos, emit_rows=emit)
         ids = list(range(B))
-        cur = e.rules_argmax(logits, tr._rules_dev(rs.rules_array(ids))).tolist()
-        n_tok, steps = 0, 0
+        e.ts_reset(ids, [int(g) for g in g_len])
+        e.ts_first(logits, ids)
+        steps = 0
         while ids:
-            done = rs.update(ids, cur)
-            n_tok += len(ids)
-            keep = [i for i, d in zip(range(len(ids)), done) if not d]
-            ids = [ids[i] for i in keep]
-            last = [cur[i] for i in keep]
-            if not ids:
-                break
-            cur = e.decode_step(last, ids, rules=tr._rules_dev(rs.rules_array(ids))).tolist()
-            steps += 1
+            e.ts_steps(ids, 8)
+            steps += 8
+            st = e.ts_poll()
+            ids = [i for i in ids if not st[i][6]]
+        n_tok = int(e.ts_poll()[:B, 1].sum())
         return n_tok, steps
     ms, (n_tok, steps) = _timed(run, reps=2)
     e.close()

@@ -47,3 +47,26 @@ def test_static_scratch_logmel_matches_workspace_logmel_twice():
         assert "at most 4" in str(err.value)
     finally:
         e.close()
+
+
+def test_static_scratch_logmel_needs_no_workspace():
+    """An engine that was never lent a workspace: the entry point with built-in scratch still works (and gives
+    the spectrogram of an ordinary engine), the workspace-based one reports that it has no memory to work in."""
+    from whisperdrz_b200.capi import WdzError
+    from whisperdrz_b200.engine import Engine
+    dims = ModelDimensions.from_name("test-tiny")
+    sd = init_state_dict(dims, 0)
+    bare = Engine(dims, sd, dtype=torch.float32, n_slots=2, max_clips=4, lend_workspace=False)
+    full = Engine(dims, sd, dtype=torch.float32, n_slots=2, max_clips=4)
+    try:
+        buf = torch.from_numpy(synth.clips([50, 51])).cuda()
+        for _ in range(2):
+            got = bare.logmel_static(buf)
+            torch.cuda.synchronize()
+            assert torch.equal(got, full.logmel(buf))
+        with pytest.raises(WdzError) as err:
+            bare.logmel(buf)
+        assert "WDZ_ENOMEM" in str(err.value)
+    finally:
+        bare.close()
+        full.close()

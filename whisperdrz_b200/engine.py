@@ -102,7 +102,7 @@ class Engine:
     def __init__(self, dims: ModelDimensions, state_dict: dict, dtype: torch.dtype = torch.bfloat16,
                  device: str | torch.device = "cuda:0", n_slots: int = 32, max_tokens: int | None = None,
                  max_clips: int = 16, max_rows: int | None = None, flags: int = 0,
-                 tables: torch.Tensor | None = None):
+                 tables: torch.Tensor | None = None, lend_workspace: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("whisperdrz_b200.Engine needs a CUDA device (no CPU path exists)")
         if dtype not in _TORCH_DTYPE:
@@ -154,10 +154,14 @@ class Engine:
             self._bind(name, t)
         if self.tables_dev is not None:
             self._bind("rules.tables", self.tables_dev)
-        need = C.c_size_t()
-        self._check(self.lib.wdz_workspace_bytes(self.h, C.byref(need)))
-        self.workspace = torch.empty(need.value, dtype=torch.uint8, device=dev)
-        self._check(self.lib.wdz_set_workspace(self.h, self.workspace.data_ptr(), need.value))
+        # lend_workspace=False: a host with no scratch memory to give; only the entry points that bring their own
+        # scratch (logmel_static) work then, the others answer WDZ_ENOMEM
+        self.workspace = None
+        if lend_workspace:
+            need = C.c_size_t()
+            self._check(self.lib.wdz_workspace_bytes(self.h, C.byref(need)))
+            self.workspace = torch.empty(need.value, dtype=torch.uint8, device=dev)
+            self._check(self.lib.wdz_set_workspace(self.h, self.workspace.data_ptr(), need.value))
         self._check(self.lib.wdz_finalize(self.h))
 
     # ------------------------------------------------------------------ util
