@@ -251,7 +251,7 @@ def main():
     dims = ModelDimensions.from_name(args.model)
     sd = init_state_dict(dims, 0)
     eng = Engine(dims, sd, dtype=torch.bfloat16, device=dev, n_slots=args.clips, max_clips=min(args.max_clips, args.clips),
-                 max_rows=max(args.clips, 64, 4096 if args.align else 0),
+                 max_rows=max(args.clips, 128, 4096 if args.align else 0),
                  tables=timestamp_tables(dims.n_vocab))
     audio_host = torch.from_numpy(synth.clips([1000 * rank + i + 1 for i in range(args.clips)])).pin_memory()
     audio_dev = audio_host.to(dev)

@@ -255,6 +255,11 @@ class Transcriber:
         """Prompt rows of slots whose cross K/V are in place (or come with ``xa``), and their first token, on
         the current stream."""
         eng = self.engine
+        cap = max(1, getattr(eng, "max_rows", 1 << 30) // max(1, len(self.init_tokens)))
+        if len(grp) > cap:                 # more prompt rows than one forward call takes
+            for i in range(0, len(grp), cap):
+                self._first_tokens(grp[i: i + cap], None if xa is None else xa[i: i + cap])
+            return
         ids = [s.index for s in grp]
         if xa is not None:
             logits = eng.prefill(xa, ids, [self.init_tokens] * len(grp))
