@@ -314,8 +314,8 @@ def main():
     peak, peak_kind = peaks()
     ca = prof["cross_attn"]
     # dram read+write per row per launch of this kernel from an ncu capture of a 32-row launch
-    # (245.944 MB read + 4.606 MB written); every row has its own K/V, so traffic grows linearly with rows
-    traffic_per_row = (245.944064e6 + 4.605952e6) / 32
+    # (245.972 MB read + 4.381 MB written); every row has its own K/V, so traffic grows linearly with rows
+    traffic_per_row = (245.971712e6 + 4.381184e6) / 32
     per_launch_ms = ca["ms"] / max(ca["launches"], 1)
     per_launch_bytes = ca["work"] / max(ca["launches"], 1)
     achieved = per_launch_bytes / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms > 0 else 0.0
