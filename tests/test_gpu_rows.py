@@ -136,8 +136,9 @@ def test_large_v3_bf16_ragged_rows_32_and_384(large, golden):
     # slots to their prompts and decode 8 tokens each way.  The bf16 step is not bit-reproducible (K-split
     # partial sums meet in fp32 atomics, and a last-bit difference can flip a bf16 rounding further down),
     # so a free-running row now and then takes another of two near-equal logits - replicas of one row do
-    # that within a single run, too.  Required: the first two tokens of every row agree and at least 80 % of
-    # the rows agree on all eight (a wrong slot, position or rule on either path would leave none).
+    # that within a single run, too.  Required: the first token of every row agrees (it comes from the same prefill
+    # logits), 95 % of the rows agree on the first two and at least 80 % on all eight (a wrong slot, position or
+    # rule on either path would leave none).
     n_new = 8
     lens0 = torch.tensor([len(p) for p in prompts] * (1 + REPLICAS), dtype=torch.int32).cuda()
     first = logits0.repeat(REPLICAS, 1)
@@ -169,7 +170,8 @@ def test_large_v3_bf16_ragged_rows_32_and_384(large, golden):
         return {s: e.ts_tokens(s, int(st[s][1])) for s in slots_big}
 
     a, b = host_path(), device_path()
-    assert all(a[s][:2] == b[s][:2] for s in slots_big)
+    assert all(a[s][:1] == b[s][:1] for s in slots_big)                                # same logits, same rule: no slack
+    assert sum(a[s][:2] == b[s][:2] for s in slots_big) >= 0.95 * len(slots_big)
     assert sum(a[s] == b[s] for s in slots_big) >= 0.8 * len(slots_big)
     assert all(len(b[s]) == n_new or b[s][-1] == TOK_EOT for s in slots_big)
     e.device_status()
