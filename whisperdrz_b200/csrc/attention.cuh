@@ -131,6 +131,7 @@ struct AttnDecParams {
   int layer, n_slots, S, d;         // cache [layers, n_slots, S, d]
   const int* slots; const int* positions; int fixed_len;  // len = positions ? positions[r] + 1 : fixed_len
   int chunk, max_splits;
+  int rows;                         // rows of the launch (the persistent kernel walks max_splits x rows items)
   float* part_o; float* part_ml;    // [rows, max_splits, H, 64] and [rows, max_splits, H, 2]
   void* out; int64_t ldo;           // combine: out (TO) + r * ldo + h * 64
   int* counters;                    // [rows], zero between launches: split CTAs of a row count themselves in, the
@@ -277,6 +278,7 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
   constexpr int KPI = 32 / LPK;
   constexpr int SK = 2 * KPI;      // keys per stage: one consumer iteration
   extern __shared__ __align__(128) uint8_t att_smem[];
+  __shared__ int s_last;
   const int H = (blockDim.x >> 5) - 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t half_bytes = (size_t)SK * p.d * sizeof(T);          // K (or V) bytes of one stage
@@ -286,17 +288,6 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * ATT_STAGES);
 
   pdl_trigger();
-  pdl_wait();
-  const int r = blockIdx.y, split = blockIdx.x;
-  const int slot = p.slots[r];
-  int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
-  len = len > p.S ? p.S : len;
-  const int start = split * p.chunk;
-  const bool active = slot >= 0 && slot < p.n_slots && start < len;   // uniform over the CTA
-  if (!active) return;
-  const int end = min(len, start + p.chunk);
-  const int n_iter = (end - start + SK - 1) / SK;
-
   if (threadIdx.x == 0) {
     for (int i = 0; i < ATT_STAGES; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(att_smem_u32(full + i)), "r"(1));
@@ -306,25 +297,44 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  pdl_wait();
 
-  const int64_t row_base = (((int64_t)p.layer * p.n_slots + slot) * p.S) * p.d;
+  // Persistent: the CTA walks the work items (key range `split` of row r; split-major, so that the ranges every
+  // row has come first) that fall to it, and the ring keeps running across items - the producer is already
+  // fetching the next item's keys while the head warps finish the current one.  `it` counts ring stages over the
+  // whole walk; producer and consumers step through the same items, so they agree on it.
+  const int n_items = p.max_splits * p.rows;
+  int it = 0;
   if (warp == H) {
     if (lane == 0) {
-      const T* Kg = reinterpret_cast<const T*>(p.cache_k) + row_base;
-      const T* Vg = reinterpret_cast<const T*>(p.cache_v) + row_base;
-      for (int it = 0; it < n_iter; ++it) {
-        const int stage = it % ATT_STAGES;
-        const uint32_t phase = (it / ATT_STAGES) & 1;
-        if (!att_mbar_wait(empty + stage, phase ^ 1, abort_flag, status)) break;
-        const int t = start + it * SK;
-        const uint32_t bytes = (uint32_t)((size_t)min(SK, end - t) * p.d * sizeof(T));
-        uint8_t* dstk = att_smem + (size_t)stage * 2 * half_bytes;
-        const uint32_t bar = att_smem_u32(full + stage);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(att_smem_u32(dstk)), "l"(Kg + (int64_t)t * p.d), "r"(bytes), "r"(bar) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(att_smem_u32(dstk + half_bytes)), "l"(Vg + (int64_t)t * p.d), "r"(bytes), "r"(bar) : "memory");
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const int split = item / p.rows, r = item - split * p.rows;
+        const int slot = p.slots[r];
+        int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
+        len = len > p.S ? p.S : len;
+        const int start = split * p.chunk;
+        if (slot < 0 || slot >= p.n_slots || start >= len) continue;
+        const int end = min(len, start + p.chunk);
+        const int n_iter = (end - start + SK - 1) / SK;
+        const int64_t row_base = (((int64_t)p.layer * p.n_slots + slot) * p.S) * p.d;
+        const T* Kg = reinterpret_cast<const T*>(p.cache_k) + row_base;
+        const T* Vg = reinterpret_cast<const T*>(p.cache_v) + row_base;
+        bool ok = true;
+        for (int j = 0; j < n_iter; ++j, ++it) {
+          const int stage = it % ATT_STAGES;
+          const uint32_t phase = (it / ATT_STAGES) & 1;
+          if (!(ok = att_mbar_wait(empty + stage, phase ^ 1, abort_flag, status))) break;
+          const int t = start + j * SK;
+          const uint32_t bytes = (uint32_t)((size_t)min(SK, end - t) * p.d * sizeof(T));
+          uint8_t* dstk = att_smem + (size_t)stage * 2 * half_bytes;
+          const uint32_t bar = att_smem_u32(full + stage);
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(att_smem_u32(dstk)), "l"(Kg + (int64_t)t * p.d), "r"(bytes), "r"(bar) : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(att_smem_u32(dstk + half_bytes)), "l"(Vg + (int64_t)t * p.d), "r"(bytes), "r"(bar) : "memory");
+        }
+        if (!ok) break;
       }
     }
     return;
@@ -332,93 +342,108 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
 
   const int h = warp;
   const int piece = lane % LPK, grp = lane / LPK;
-  float qv[VEC];
-  {
-    const float* qp = p.q + (int64_t)r * p.ldq + h * HD + piece * VEC;
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) qv[e] = qp[e] * QK_SCALE_LOG2E;
-  }
-  float m = -INFINITY, l = 0.0f, o[VEC];
-#pragma unroll
-  for (int e = 0; e < VEC; ++e) o[e] = 0.0f;
   const int col = h * HD + piece * VEC;
-  bool ok = true;
-  for (int it = 0; it < n_iter; ++it) {
-    const int stage = it % ATT_STAGES;
-    const uint32_t phase = (it / ATT_STAGES) & 1;
-    ok = att_mbar_wait(full + stage, phase, abort_flag, status);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) break;
-    const T* Ks = reinterpret_cast<const T*>(att_smem + (size_t)stage * 2 * half_bytes);
-    const T* Vs = reinterpret_cast<const T*>(att_smem + (size_t)stage * 2 * half_bytes + half_bytes);
-    const int t0 = start + it * SK;
-    const bool va = t0 + grp < end, vb = t0 + KPI + grp < end;
-    float ka[VEC], kb[VEC], xa[VEC], xb[VEC];
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int split = item / p.rows, r = item - split * p.rows;
+    const int slot = p.slots[r];
+    int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
+    len = len > p.S ? p.S : len;
+    const int start = split * p.chunk;
+    if (slot < 0 || slot >= p.n_slots || start >= len) continue;   // uniform over the CTA
+    const int end = min(len, start + p.chunk);
+    const int n_iter = (end - start + SK - 1) / SK;
+    float qv[VEC];
+    {
+      const float* qp = p.q + (int64_t)r * p.ldq + h * HD + piece * VEC;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) ka[e] = kb[e] = xa[e] = xb[e] = 0.0f;
-    if (va) { load_vec(Ks + (size_t)grp * p.d + col, ka); load_vec(Vs + (size_t)grp * p.d + col, xa); }
-    if (vb) { load_vec(Ks + (size_t)(KPI + grp) * p.d + col, kb); load_vec(Vs + (size_t)(KPI + grp) * p.d + col, xb); }
-    __syncwarp();
-    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(att_smem_u32(empty + stage)) : "memory");
-    float sa = 0.0f, sb = 0.0f;
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) { sa = fmaf(qv[e], ka[e], sa); sb = fmaf(qv[e], kb[e], sb); }
-#pragma unroll
-    for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) {
-      sa += __shfl_xor_sync(0xffffffffu, sa, o2);
-      sb += __shfl_xor_sync(0xffffffffu, sb, o2);
+      for (int e = 0; e < VEC; ++e) qv[e] = qp[e] * QK_SCALE_LOG2E;
     }
-    if (!va) sa = -INFINITY;
-    if (!vb) sb = -INFINITY;
-    const float m_new = fmaxf(m, fmaxf(sa, sb));
-    if (m_new > -INFINITY) {
-      const float alpha = exp2f(m - m_new);
-      const float pa = exp2f(sa - m_new), pb = exp2f(sb - m_new);
-      l = l * alpha + pa + pb;
+    float m = -INFINITY, l = 0.0f, o[VEC];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) o[e] = fmaf(pb, xb[e], fmaf(pa, xa[e], o[e] * alpha));
+    for (int e = 0; e < VEC; ++e) o[e] = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_iter; ++j, ++it) {
+      const int stage = it % ATT_STAGES;
+      const uint32_t phase = (it / ATT_STAGES) & 1;
+      ok = att_mbar_wait(full + stage, phase, abort_flag, status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const T* Ks = reinterpret_cast<const T*>(att_smem + (size_t)stage * 2 * half_bytes);
+      const T* Vs = reinterpret_cast<const T*>(att_smem + (size_t)stage * 2 * half_bytes + half_bytes);
+      const int t0 = start + j * SK;
+      const bool va = t0 + grp < end, vb = t0 + KPI + grp < end;
+      float ka[VEC], kb[VEC], xa[VEC], xb[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) ka[e] = kb[e] = xa[e] = xb[e] = 0.0f;
+      if (va) { load_vec(Ks + (size_t)grp * p.d + col, ka); load_vec(Vs + (size_t)grp * p.d + col, xa); }
+      if (vb) { load_vec(Ks + (size_t)(KPI + grp) * p.d + col, kb); load_vec(Vs + (size_t)(KPI + grp) * p.d + col, xb); }
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(att_smem_u32(empty + stage)) : "memory");
+      float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { sa = fmaf(qv[e], ka[e], sa); sb = fmaf(qv[e], kb[e], sb); }
+#pragma unroll
+      for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) {
+        sa += __shfl_xor_sync(0xffffffffu, sa, o2);
+        sb += __shfl_xor_sync(0xffffffffu, sb, o2);
+      }
+      if (!va) sa = -INFINITY;
+      if (!vb) sb = -INFINITY;
+      const float m_new = fmaxf(m, fmaxf(sa, sb));
+      if (m_new > -INFINITY) {
+        const float alpha = exp2f(m - m_new);
+        const float pa = exp2f(sa - m_new), pb = exp2f(sb - m_new);
+        l = l * alpha + pa + pb;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = fmaf(pb, xb[e], fmaf(pa, xa[e], o[e] * alpha));
+        m = m_new;
+      }
+    }
+    // (after an exhausted wait the warps still meet at the barrier below and leave together from there)
+#pragma unroll
+    for (int o2 = LPK; o2 < 32; o2 <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o2);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l, o2);
+      const float m_new = fmaxf(m, m2);
+      const float a1 = m_new > -INFINITY ? exp2f(m - m_new) : 0.0f;
+      const float a2 = m_new > -INFINITY ? exp2f(m2 - m_new) : 0.0f;
+      l = l * a1 + l2 * a2;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float o2v = __shfl_xor_sync(0xffffffffu, o[e], o2);
+        o[e] = o[e] * a1 + o2v * a2;
+      }
       m = m_new;
     }
-  }
-  if (!ok && !p.counters) return;
+    const int64_t pi = ((int64_t)r * p.max_splits + split) * H + h;
+    if (grp == 0) {
 #pragma unroll
-  for (int o2 = LPK; o2 < 32; o2 <<= 1) {
-    const float m2 = __shfl_xor_sync(0xffffffffu, m, o2);
-    const float l2 = __shfl_xor_sync(0xffffffffu, l, o2);
-    const float m_new = fmaxf(m, m2);
-    const float a1 = m_new > -INFINITY ? exp2f(m - m_new) : 0.0f;
-    const float a2 = m_new > -INFINITY ? exp2f(m2 - m_new) : 0.0f;
-    l = l * a1 + l2 * a2;
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      const float o2v = __shfl_xor_sync(0xffffffffu, o[e], o2);
-      o[e] = o[e] * a1 + o2v * a2;
+      for (int e = 0; e < VEC; ++e) p.part_o[pi * HD + piece * VEC + e] = o[e];
     }
-    m = m_new;
-  }
-  const int64_t pi = ((int64_t)r * p.max_splits + split) * H + h;
-  if (grp == 0) {
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) p.part_o[pi * HD + piece * VEC + e] = o[e];
-  }
-  if (lane == 0) { p.part_ml[pi * 2] = m; p.part_ml[pi * 2 + 1] = l; }
-  if (!p.counters) return;
-  // The split CTAs of a row count themselves in; whichever comes last finds all partial results in place and
-  // merges them, so no combine launch is needed and nobody waits for anybody.  (After an exhausted wait the
-  // CTA still counts itself in: the status word already tells the host that the output is void.)
-  __shared__ int s_last;
-  __threadfence();
-  asm volatile("bar.sync 1, %0;" ::"r"(H * 32) : "memory");          // the H head warps; the producer warp has left
-  if (threadIdx.x == 0) {
+    if (lane == 0) { p.part_ml[pi * 2] = m; p.part_ml[pi * 2 + 1] = l; }
+    // The items of a row count themselves in; whichever comes last finds all partial results in place and merges
+    // them, so no combine launch is needed and nobody waits for anybody.
     const int nsplit = (len + p.chunk - 1) / p.chunk;
-    const int old = atomicAdd(p.counters + r, 1);
-    s_last = old == nsplit - 1;
-    if (s_last) p.counters[r] = 0;                                   // ready for the next launch
+    __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"r"(H * 32) : "memory");          // the H head warps; the producer warp is not part of it
+    if (threadIdx.x == 0) {
+      if (*abort_flag) {
+        s_last = -1;      // a wait ran out somewhere in this CTA: the status word tells the host that the output is
+                          // void (it clears the arrival counters when it reads that status); everybody leaves
+      } else {
+        const int old = atomicAdd(p.counters + r, 1);
+        s_last = old == nsplit - 1;
+        if (s_last) p.counters[r] = 0;                                 // ready for the next launch
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(H * 32) : "memory");
+    const int last = s_last;
+    if (last < 0) return;
+    if (last) {
+      __threadfence();
+      attn_dec_merge_head<T>(p, r, h, lane, H, nsplit);
+    }
   }
-  asm volatile("bar.sync 1, %0;" ::"r"(H * 32) : "memory");
-  if (!s_last) return;
-  __threadfence();
-  attn_dec_merge_head<T>(p, r, h, lane, H, (len + p.chunk - 1) / p.chunk);
 }
 
 template <typename T>

@@ -389,15 +389,21 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
   const int H = e->cfg.n_text_head;
   const bool stream = e->stream_attn_ok;
   int splits;
+  // The streaming kernel walks (key range, row) items.  With few rows one persistent CTA per SM takes several items
+  // and keeps its ring running across them (a 32-row step has only a wave or two of items, and every fresh CTA pays
+  // the ring's start); with many rows one CTA per item does better, because a finished CTA's successor starts on
+  // the hardware's own schedule while an item change inside a CTA stalls its head warps on the next query.
+  const bool persistent = stream && rows < 128;
   if (stream && !cross) {
-    p.chunk = 128;   // lengths are only known on the device: fixed ranges, CTAs past a row's length exit at once
+    // lengths are only known on the device: fixed ranges, items past a row's length are skipped
+    p.chunk = persistent ? 64 : 128;
   } else if (stream) {
-    // one CTA per SM at a time: pick the split count that fills whole waves best
+    // pick the split count whose items fill the SMs most evenly (whole waves of CTAs, or equal shares per CTA)
     int best = 1;
     double best_util = 0.0;
     for (int c = 1; c <= (rows <= 4 ? 46 : 24) && (int64_t)rows * c <= e->part_entries && max_len / c >= 32; ++c) {
-      const int ctas = rows * c, waves = (ctas + e->sm_count - 1) / e->sm_count;
-      const double util = (double)ctas / ((double)waves * e->sm_count);
+      const int items = rows * c, per_cta = (items + e->sm_count - 1) / e->sm_count;
+      const double util = (double)items / ((double)per_cta * e->sm_count);
       if (util > best_util + 0.03) { best_util = util; best = c; }
     }
     p.chunk = (max_len + best - 1) / best;
@@ -416,8 +422,11 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
   const int sp = e->span_begin(cross ? WDZ_PROF_CROSS_ATTN : WDZ_PROF_SELF_ATTN,
                                cross ? 2.0 * rows * max_len * p.d * sizeof(T) : 0.0, s);
   if (stream) {
-    p.counters = e->att_counters;   // the last split CTA of a row merges the row: no combine launch
-    launch_pdl(e, attn_dec_stream_kernel<T>, dim3(splits, rows), dim3((H + 1) * 32), attn_dec_stream_smem<T>(p.d), s, p, e->status);
+    p.counters = e->att_counters;   // the last item of a row merges the row: no combine launch
+    p.rows = rows;
+    const int items = splits * rows;
+    launch_pdl(e, attn_dec_stream_kernel<T>, dim3(persistent && items > e->sm_count ? e->sm_count : items), dim3((H + 1) * 32),
+               attn_dec_stream_smem<T>(p.d), s, p, e->status);
     e->span_end(sp, s);
     WDZ_LAUNCH_CHECK(e, "attn_dec_stream");
     return WDZ_OK;
