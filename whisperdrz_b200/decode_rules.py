@@ -335,6 +335,33 @@ def compile_row(r: RowRules, t: RuleTables, penalty: bool = True) -> dict:
     return rule
 
 
+def rows_from_decode_batch(loc: dict, rows=None, timing_ranges: dict | None = None) -> list[RowRules]:
+    """``RowRules`` of the sampled rows from the local variables of the reference's ``decode_batch`` as they
+    stand when its Phase 1.5 is done (decoding.py:1512): every ``*_indices`` list is a constraint group, plus the
+    two derived lists that carry no suffix.  ``rows``: the batch rows wanted (default ``need_sampling``);
+    ``timing_ranges``: row -> (s_idx, e_idx) of ``_get_timing_range_cpu`` for the special-timing rows (the
+    reference computes them inside its Phase 2 loop, :1698-1713)."""
+    groups = {k[: -len("_indices")]: set(v) for k, v in loc.items() if k.endswith("_indices") and isinstance(v, list)}
+    for k in ("block_asterisk_combined", "block_bracket_after_close"):
+        groups[k] = set(loc.get(k, ()))
+    special = set().union(*(groups.get(n, set()) for n in SPECIAL_TIMING))
+    forced_close = set(loc.get("forced_close_indices", ()))
+    states, contexts, counts = loc["states"], loc["contexts"], loc["token_counts"]
+    out = []
+    for i in (loc["need_sampling"] if rows is None else rows):
+        ctx = contexts[i]
+        line = ctx.get("line", "") or ""
+        pen = ()
+        if i not in special and i not in forced_close and counts[i] > 0:                 # decoding.py:1734-1740
+            pen = tuple(set(states[i].recent_tokens))
+        out.append(RowRules(
+            groups=frozenset(g for g, members in groups.items() if i in members),
+            language=getattr(states[i], "language", None), last_timing=ctx.get("last_timing"),
+            bracket_partial=line[line.rfind("[") + 1:] if i in groups.get("in_bracket", ()) else "",
+            timing_range=(timing_ranges or {}).get(i), penalty_ids=pen))
+    return out
+
+
 def compile_rows(rows: list[RowRules], t: RuleTables) -> np.ndarray:
     """int32 [len(rows), 32] in ``wdz_rule_desc`` layout."""
     from .transcriber import rules_to_array
