@@ -216,6 +216,21 @@ class Engine:
         return res
 
     # ------------------------------------------------------------- front end
+    def _checked_lengths(self, N: int, B: int, n_samples) -> torch.Tensor:
+        """Per-clip sample counts as a device tensor; lengths that come from the host are validated there, so that
+        the call does not have to wait for the GPU (a device tensor is read back once)."""
+        if n_samples is None:
+            shortest, ns = N, self._i32([N] * B)
+        elif isinstance(n_samples, torch.Tensor):
+            ns = self._i32(n_samples)
+            shortest = int(ns.min())
+        else:
+            host = [int(v) for v in n_samples]
+            shortest, ns = min(host), self._i32(host)
+        if shortest < 400:
+            raise ValueError("clips shorter than 400 samples cannot be reflect-padded")
+        return ns
+
     def logmel(self, audio: torch.Tensor, n_samples=None, frame_offset=None) -> torch.Tensor:
         """audio f32 [B, N] (device) -> mel f32 [B, n_mels, 3000]."""
         audio = audio.to(device=self.device, dtype=torch.float32)
@@ -225,9 +240,7 @@ class Engine:
         B, N = audio.shape
         if N > 480000:
             raise ValueError("a window holds at most 30 s (480000 samples)")
-        ns = self._i32([N] * B if n_samples is None else n_samples)
-        if int(ns.min()) < 400:
-            raise ValueError("clips shorter than 400 samples cannot be reflect-padded")
+        ns = self._checked_lengths(N, B, n_samples)
         fo = None if frame_offset is None else self._i32(frame_offset)
         mel = torch.empty(B, self.dims.n_mels, 3000, dtype=torch.float32, device=self.device)
         self._check(self.lib.wdz_logmel(self.h, audio.data_ptr(), N, ns.data_ptr(),
@@ -248,9 +261,7 @@ class Engine:
         B, N = audio.shape
         if N > 480000:
             raise ValueError("a window holds at most 30 s (480000 samples)")
-        ns = self._i32([N] * B if n_samples is None else n_samples)
-        if int(ns.min()) < 400:
-            raise ValueError("clips shorter than 400 samples cannot be reflect-padded")
+        ns = self._checked_lengths(N, B, n_samples)
         fo = None if frame_offset is None else self._i32(frame_offset)
         mel = torch.empty(B, self.dims.n_mels, 3000, dtype=torch.float32, device=self.device)
         self._check(self.lib.wdz_logmel_static(self.h, audio.data_ptr(), N, ns.data_ptr(),
