@@ -424,6 +424,30 @@ def test_transcribe_end_to_end_identical_to_oracle_scheduler():
     e.close()
 
 
+def test_load_model_entry_point_and_warm_slots():
+    """``whisperdrz_b200.load_model`` (the shape of the reference's ``whisperdrz.load_model``,
+    __init__.py:9-22) gives a ready Transcriber; with a warm pool (log-mel, encoder and cross K/V of the next
+    chunks on a side stream, event-gated promotion) it returns the tokens of the plain scheduler."""
+    import whisperdrz_b200
+    audio = torch.from_numpy(synth.long_form(6, 100.0))          # 4 chunks
+    kw = dict(dtype=torch.float32, max_clips=2, max_new_tokens=16, max_continuations=0, dtw_align=True,
+              align_heads=[(0, 1), (1, 0), (1, 3)])
+    plain = whisperdrz_b200.load_model("test-small", n_slots=2, **kw)
+    want = plain.transcribe(audio)
+    plain.engine.device_status()
+    assert [r["id"] for r in want.raw_chunks] == [f"chunk_{i}" for i in range(4)]
+    assert all(r["tokens"] and r["stop_reason"] in ("eot", "max_tokens") for r in want.raw_chunks)
+    assert all("word_times" in r for r in want.raw_chunks)      # dtw_align=True: token-level word timing
+    plain.engine.close()
+    warm = whisperdrz_b200.load_model("test-small", n_slots=4, n_warm=2, **kw)
+    got = warm.transcribe(audio)
+    warm.engine.device_status()
+    assert warm.promoted == 4 and warm.prefill_stream is not None
+    assert [r["tokens"] for r in got.raw_chunks] == [r["tokens"] for r in want.raw_chunks]
+    assert [r["word_times"] for r in got.raw_chunks] == [r["word_times"] for r in want.raw_chunks]
+    warm.engine.close()
+
+
 @pytest.mark.parametrize("M,N", [(1, 1280), (8, 1280), (16, 1280), (40, 1280), (256, 1280), (300, 1280),
                                  (100, 1280), (200, 1280), (200, 3840), (129, 5120), (72, 2000)])
 def test_decode_shaped_linear_matches_fp32_reference(small_bf16, M, N):

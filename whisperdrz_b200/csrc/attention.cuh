@@ -131,7 +131,9 @@ struct AttnDecParams {
   int layer, n_slots, S, d;         // cache [layers, n_slots, S, d]
   const int* slots; const int* positions; int fixed_len;  // len = positions ? positions[r] + 1 : fixed_len
   int chunk, max_splits;
-  int rows;                         // rows of the launch (the persistent kernel walks max_splits x rows items)
+  int rows;                         // rows of the launch (the kernel walks max_splits x rows items)
+  int split_major;                  // item order: 1 = all rows of range 0, then range 1, ... (persistent walk: the ranges
+                                    // every row has come first); 0 = the ranges of a row side by side (one CTA per item)
   float* part_o; float* part_ml;    // [rows, max_splits, H, 64] and [rows, max_splits, H, 2]
   void* out; int64_t ldo;           // combine: out (TO) + r * ldo + h * 64
   int* counters;                    // [rows], zero between launches: split CTAs of a row count themselves in, the
@@ -288,6 +290,18 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * ATT_STAGES);
 
   pdl_trigger();
+  const int n_items = p.max_splits * p.rows;
+  const bool one_item = (int)gridDim.x >= n_items;   // one CTA per item: most self-attention items lie past their
+  if (one_item) {                                    // row's length, and those CTAs should leave before any set-up
+    pdl_wait();
+    const int item = blockIdx.x;
+    const int split = p.split_major ? item / p.rows : item % p.max_splits;
+    const int r = p.split_major ? item - split * p.rows : item / p.max_splits;
+    const int slot = p.slots[r];
+    int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
+    len = len > p.S ? p.S : len;
+    if (slot < 0 || slot >= p.n_slots || split * p.chunk >= len) return;
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < ATT_STAGES; ++i) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(att_smem_u32(full + i)), "r"(1));
@@ -297,18 +311,18 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();
+  if (!one_item) pdl_wait();     // the persistent walk sets its ring up while the previous kernel drains
 
-  // Persistent: the CTA walks the work items (key range `split` of row r; split-major, so that the ranges every
-  // row has come first) that fall to it, and the ring keeps running across items - the producer is already
+  // The CTA walks the work items (key range `split` of row r) that fall to it - all of them when the grid is one
+  // CTA per SM, exactly one when the grid is one CTA per item - and the ring keeps running across items: the producer is already
   // fetching the next item's keys while the head warps finish the current one.  `it` counts ring stages over the
   // whole walk; producer and consumers step through the same items, so they agree on it.
-  const int n_items = p.max_splits * p.rows;
   int it = 0;
   if (warp == H) {
     if (lane == 0) {
       for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int split = item / p.rows, r = item - split * p.rows;
+        const int split = p.split_major ? item / p.rows : item % p.max_splits;
+        const int r = p.split_major ? item - split * p.rows : item / p.max_splits;
         const int slot = p.slots[r];
         int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
         len = len > p.S ? p.S : len;
@@ -344,7 +358,8 @@ __global__ void __launch_bounds__(672, 1) attn_dec_stream_kernel(AttnDecParams p
   const int piece = lane % LPK, grp = lane / LPK;
   const int col = h * HD + piece * VEC;
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const int split = item / p.rows, r = item - split * p.rows;
+    const int split = p.split_major ? item / p.rows : item % p.max_splits;
+        const int r = p.split_major ? item - split * p.rows : item / p.max_splits;
     const int slot = p.slots[r];
     int len = p.positions ? p.positions[r] + 1 : p.fixed_len;
     len = len > p.S ? p.S : len;

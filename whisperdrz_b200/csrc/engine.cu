@@ -424,6 +424,7 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
   if (stream) {
     p.counters = e->att_counters;   // the last item of a row merges the row: no combine launch
     p.rows = rows;
+    p.split_major = persistent ? 1 : 0;
     const int items = splits * rows;
     launch_pdl(e, attn_dec_stream_kernel<T>, dim3(persistent && items > e->sm_count ? e->sm_count : items), dim3((H + 1) * 32),
                attn_dec_stream_smem<T>(p.d), s, p, e->status);
