@@ -144,6 +144,40 @@ def test_forward_flash_inside_a_cuda_graph(refmod, small):
     m.engine.close()
 
 
+def test_large_v3_bf16_dropin_runs_faster_than_real_time(refmod, capsys):
+    """The reference's scheduler over the full-size bf16 engine (``dropin.bind``: engine log-mel, engine step graph):
+    five minutes of long-form audio, 32 slots, word timing off.  With random weights the reference's own stop rules
+    end windows after a few dozen tokens and re-encode continuation windows up to twenty times per chunk, and its
+    ``decode_batch`` classifies every row on the host at every step, so this is a floor, not a throughput claim:
+    the run must finish well ahead of real time.  The measured figure is printed (pytest -s)."""
+    import time
+    dims = ModelDimensions.from_name("large-v3")
+    sd = init_state_dict(dims, 0)
+    from whisperdrz.transcriber import Transcriber
+    from whisperdrz_b200 import dropin
+    from whisperdrz_b200.model import B200Model
+    from whisperdrz.tokenizer import get_tokenizer
+    model = B200Model(dims, sd, dtype=torch.bfloat16, tokenizer=get_tokenizer(True, num_languages=100, language="en"),
+                      max_clips=16)
+    t = Transcriber(model_path=None, model=model, lang="en", speaker_remap=False, BS=32, dtw_align=False)
+    dropin.bind(t)
+    audio = torch.from_numpy(synth.long_form(12, 300.0))
+    t.transcribe(audio[: 16000 * 30])                            # warm-up: graphs, tables
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = t.transcribe(audio)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    model.engine.device_status()
+    assert len(res.raw_chunks) == 10 and all(r.get("stop_reason") for r in res.raw_chunks)
+    windows = sum(1 + (r.get("prediction") or "").count("[CHOP]") for r in res.raw_chunks)
+    with capsys.disabled():
+        print(f"\n[drop-in, large-v3 bf16, 32 slots] 300 s of audio in {dt:.2f} s = {300.0 / dt:.1f}x real time "
+              f"({windows} windows, {sum(t.cuda_graphs.hits.values())} decode steps)")
+    assert 300.0 / dt > 10.0
+    model.engine.close()
+
+
 TS = re.compile(r"<\|(\d+\.\d+)\|>")
 
 
