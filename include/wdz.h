@@ -109,8 +109,8 @@ int wdz_set_workspace(wdz_engine* e, void* dev, size_t bytes);
  *   cache.cross_k / cache.cross_v [n_text_layer, n_slots, n_audio_ctx, n_text_state]
  *   cache.seq_lens                int32 [n_slots]
  * (FlashKVCache, model.py:98-147, one allocation per kind instead of one
- * object per layer) and rules.tables uint32 [WDZ_MAX_TABLES, ceil(n_vocab/32)]
- * (the [V] bool class masks of DecoderState, decoding.py:397-724, as bitsets). */
+ * object per layer) and rules.tables uint32 [n_tables >= WDZ_MAX_TABLES, ceil(n_vocab/32)]
+ * (the [V] bool class masks of DecoderState, decoding.py:397-724, as bitsets; optional). */
 int wdz_bind(wdz_engine* e, const char* name, const void* dev, int64_t numel);
 int wdz_finalize(wdz_engine* e);
 const char* wdz_last_error(const wdz_engine* e);
