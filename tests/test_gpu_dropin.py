@@ -110,6 +110,19 @@ def test_bf16_engine_under_the_reference_scheduler(refmod, small, audio, cpu_res
     assert sum(t.cuda_graphs.hits.values()) > 20
 
 
+def test_model_seam_alone_without_bind(refmod, small, audio, cpu_result):
+    """``Transcriber(model=B200Model(...))`` with nothing else touched: the reference computes log-mel on the CPU
+    and, where flash-attn is importable, captures ``forward_flash`` into its bucketed CUDA graphs (the capture then
+    holds the engine's kernels).  Its bucket padding re-runs stale rows - the reference's own hazard, which
+    ``bind`` removes - so only the structure of the result is checked here."""
+    dims, sd = small
+    t = _b200_transcriber(refmod, dims, sd, bind=False, dtw_align=False)
+    got = t.transcribe(audio)
+    t.model.engine.device_status()
+    assert [r["id"] for r in got.raw_chunks] == [r["id"] for r in cpu_result.raw_chunks]
+    assert all(r.get("stop_reason") and "prediction" in r for r in got.raw_chunks)
+
+
 def test_forward_flash_inside_a_cuda_graph(refmod, small):
     """The reference captures ``decoder.forward_flash`` into CUDA graphs when flash-attn is importable
     (transcriber.py:91-119).  Captured and replayed, the engine's step gives the logits of a direct call."""
