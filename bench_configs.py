@@ -33,7 +33,7 @@ import os
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-from whisperdrz_b200 import synth  # noqa: E402
+from whisperdrz_b200 import capi, synth  # noqa: E402
 from whisperdrz_b200.dims import ModelDimensions, TOK_EOT  # noqa: E402
 from whisperdrz_b200.engine import Engine  # noqa: E402
 from whisperdrz_b200.rules import timestamp_tables  # noqa: E402
@@ -88,8 +88,8 @@ def cfg1(dims, sd):
     return res
 
 
-def cfg2(dims, sd):
-    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=2, max_clips=16)
+def cfg2(dims, sd, flags=0):
+    e = Engine(dims, sd, dtype=torch.bfloat16, n_slots=2, max_clips=16, flags=flags)
     audio = torch.from_numpy(synth.clips(range(1, 17))).cuda()
     ms_mel, mel = _timed(lambda: e.logmel(audio))
     ms_enc, _ = _timed(lambda: e.encode(mel))
@@ -235,15 +235,42 @@ def products(dims, sd, row_counts=(32, 256), once=False):
     return out
 
 
+def enc_products(dims, sd, rows=48000, once=False):
+    """The encoder's four products on their own (bias, bf16 out; fc1 with and without its GELU), CTA pairs against
+    lone CTAs.  ``once``: the fc1 + GELU product launched a single time per kernel (for profiler captures)."""
+    small = ModelDimensions.from_name("test-small")
+    e = Engine(small, init_state_dict(small, 0), dtype=torch.bfloat16, n_slots=2, max_clips=1)
+    d = dims.n_audio_state
+    shapes = {"qkv": (3 * d, d, False), "out": (d, d, False), "fc1 + gelu": (4 * d, d, True),
+              "fc1 without gelu": (4 * d, d, False), "fc2": (d, 4 * d, False)}
+    if once:
+        shapes = {"fc1 + gelu": shapes["fc1 + gelu"]}
+    g = torch.Generator(device="cpu").manual_seed(9)
+    out = {"workload": f"encoder products, {rows} rows, bf16", "us_tflops": {}}
+    for name, (N, K, gelu) in shapes.items():
+        x = torch.randn(rows, K, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(N, K, generator=g) * 0.03).to(torch.bfloat16).cuda()
+        b = torch.zeros(N, dtype=torch.bfloat16, device="cuda")
+        for mode, label in ((0, "pairs"), (2, "lone")):
+            ms, _ = _timed(lambda: e.linear(x, w, b, gelu=gelu, cuda_cores_only=mode), reps=1 if once else 20,
+                           warm=0 if once else 3)
+            out["us_tflops"][f"{name} N{N} K{K} {label}"] = [round(ms * 1e3, 1), round(2.0 * rows * N * K / ms / 1e9, 1)]
+    e.close()
+    return out
+
+
 def main(argv):
     want = argv or ["cfg1", "cfg2", "cfg3", "cfg5"]
     dims = ModelDimensions.from_name("large-v3")
     sd = init_state_dict(dims, 0)
     fns = {"cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg5": cfg5,
+           "cfg2_lone_cta": lambda d, s: cfg2(d, s, flags=capi.FLAG_NO_CTA_PAIRS),
            "cfg5b": lambda d, s: cfg5(d, s, min_refill=8), "cfg5w": lambda d, s: cfg5(d, s, n_warm=32),
            "cfg5_small": lambda d, s: cfg5(d, s, n_req=96, offered=1500.0), "align": align,
            "align_small": lambda d, s: align(d, s, n_ids=150), "products": products,
-           "products_once": lambda d, s: products(d, s, row_counts=(256,), once=True)}
+           "products_once": lambda d, s: products(d, s, row_counts=(256,), once=True),
+           "enc_products": enc_products,
+           "enc_products_once": lambda d, s: enc_products(d, s, rows=24000, once=True)}
     with torch.inference_mode():
         for w in want:
             print(json.dumps(fns[w](dims, sd)), flush=True)

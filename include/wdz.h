@@ -55,6 +55,7 @@ typedef struct wdz_config {
 #define WDZ_FLAG_NO_TENSOR_CORE 1 /* keep bf16 GEMMs on the CUDA-core path (debug / A-B runs) */
 #define WDZ_FLAG_NO_GRAPH 4       /* launch the decode step kernel by kernel instead of replaying a CUDA graph */
 #define WDZ_FLAG_NO_PDL 8         /* decode kernels launched without programmatic dependent launch */
+#define WDZ_FLAG_NO_CTA_PAIRS 16  /* encoder-shaped GEMMs on lone CTAs (128x256 tiles) instead of CTA pairs (256x256) */
 #define WDZ_FLAG_NO_BULK_COPY 2   /* cross-attention through plain loads instead of the bulk-copy ring */
 
 /* Per-row logit rule: the device half of decode_batch
@@ -176,8 +177,9 @@ int wdz_encode(wdz_engine* e, const float* mel_dev, int B, void* xa_out_dev, wdz
 
 /* One nn.Linear (+ exact GELU when gelu != 0) in cfg.dtype, as the encoder
  * runs it (model.py:258-261, 387-393): y[M,N] = act(x[M,K] w[N,K]^T + bias).
- * bias_dev may be NULL.  cuda_cores_only != 0 keeps a bf16 product off the
- * tcgen05 kernel (for A/B checks). */
+ * bias_dev may be NULL.  cuda_cores_only (for A/B checks): 1 keeps a bf16
+ * product off the tcgen05 kernels, 2 keeps it on the lone-CTA tcgen05 kernel
+ * (no CTA pairs), 0 is the engine's own choice. */
 int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev, const void* bias_dev, int N,
                int gelu, void* y_dev, int cuda_cores_only, wdz_stream s);
 

@@ -263,6 +263,31 @@ def test_tensor_core_linear_matches_fp32_reference(small_bf16, M, N, K, gelu):
     assert err < 6e-3, err
     got_cc = e.linear(x, w, b, gelu=gelu, cuda_cores_only=True).float().cpu()
     assert (got - got_cc).abs().max() / ref.abs().max() < 6e-3
+    # the CTA-pair kernel (M > 128) and the lone-CTA kernel add the same k-blocks in the same order
+    got_lone = e.linear(x, w, b, gelu=gelu, cuda_cores_only=2).float().cpu()
+    e.device_status()
+    assert torch.equal(got, got_lone)
+
+
+def test_tensor_core_gelu_epilogue_against_exact_erf(small_bf16):
+    """The branch-free GELU of the tensor-core epilogues against 0.5 x (1 + erf(x / sqrt 2)) in float64: a 0/1 weight
+    matrix makes every output gelu(x[m, k]) of one bf16 input exactly, so what is left is the epilogue's own error
+    (below 1e-6 absolute) and the final rounding to bf16 (2^-9 relative)."""
+    e, _, _ = small_bf16
+    M, K, N = 512, 64, 256
+    x = torch.linspace(-9.0, 9.0, M * K).reshape(M, K).bfloat16()
+    w = torch.zeros(N, K)
+    w[torch.arange(N), torch.arange(N) % K] = 1.0
+    xd = x.double()[:, torch.arange(N) % K]
+    ref = 0.5 * xd * (1.0 + torch.erf(xd / 2.0 ** 0.5))
+    for mode in (0, 2):
+        got = e.linear(x, w.bfloat16(), None, gelu=True, cuda_cores_only=mode).double().cpu()
+        e.device_status()
+        err = (got - ref).abs()
+        assert bool((err <= ref.abs() * 2.0 ** -8 + 1.5e-6).all()), float((err - ref.abs() * 2.0 ** -8).max())
+        # and it lands on the correctly rounded bf16 value wherever the value is not itself of the size of that error
+        big = ref.abs() >= 1e-3
+        assert (got[big] != ref.float().bfloat16().double()[big]).double().mean() < 0.005
 
 
 def test_decoder_bf16_many_rows_tensor_core_path():

@@ -62,6 +62,31 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 
+// The same GELU, branch-free and with ONE special-function instruction, for the bf16 tensor-core epilogues (which are
+// bound by the transcendental pipe: the library erff costs ~50 instructions with both of its branches taken in a warp,
+// and a reciprocal + exponential form still saturated that pipe):
+//   erf(z) = 1 - 2^(-q(z)),  z in [0, 4],  q = the degree-7 polynomial below (no constant term), fitted here by
+//   weighted least squares to -log2(erfc(z)); beyond 4, erf is 1 to fp32 precision.
+// Absolute error of erf: 1.6e-7 with an exact 2^x, about 4e-7 with ex2.approx - the size of fp32 rounding in the
+// reference's own evaluation - so the GELU value is off by less than 1e-6 for every input, before it is rounded to
+// bf16 (2^-9 relative) or added to an O(1) fp32 stream.
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float z = x * 0.70710678118654752440f;
+  const float a = fminf(fabsf(z), 4.0f);
+  float q = -1.0020713708352587e-4f;
+  q = fmaf(q, a, 4.6149219114128025e-4f);
+  q = fmaf(q, a, 2.3024143134139e-3f);
+  q = fmaf(q, a, -2.9452696402427522e-2f);
+  q = fmaf(q, a, 1.489637594409859e-1f);
+  q = fmaf(q, a, 9.183286244618459e-1f);
+  q = fmaf(q, a, 1.6279137332204003f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-q * a));
+  const float er = copysignf(1.0f - e, z);
+  const float h = 0.5f * x;
+  return fmaf(h, er, h);
+}
+
 // Programmatic dependent launch: a kernel launched with the programmatic
 // stream-serialization attribute may start while its predecessor is still
 // running; pdl_wait() blocks until the predecessor has completed and its

@@ -26,6 +26,7 @@
 #include "align.cuh"
 #ifdef WDZ_WITH_TC
 #include "gemm_tc.cuh"
+#include "gemm_tc2.cuh"
 #include "attn_tc.cuh"
 #endif
 
@@ -62,6 +63,7 @@ struct wdz_engine {
   bool finalized = false;
   int device = 0;
   int sm_count = 148;
+  int max_pairs = 0;   // CTA pairs (clusters of two) of gemm_tc2_kernel the device runs at once; 0 = kernel unused
   size_t esz = 2;
 
   // resolved tensors
@@ -640,6 +642,17 @@ static int gemm_tc_init(wdz_engine* e) {
     cudaError_t ce = cudaGetLastError();
     return e->fail(WDZ_ECUDA, "gemm_tc smem attribute: %s", cudaGetErrorString(ce));
   }
+  // CTA-pair kernel: how many pairs the device holds at once (0 leaves every product to the lone-CTA kernel)
+  e->max_pairs = 0;
+  if (!(e->cfg.flags & WDZ_FLAG_NO_CTA_PAIRS) &&
+      cudaFuncSetAttribute(tc2::gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES) == cudaSuccess) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * e->sm_count); cfg.blockDim = dim3(tc2::THREADS); cfg.dynamicSmemBytes = tc2::SMEM_BYTES;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, tc2::gemm_tc2_kernel, &cfg) == cudaSuccess && n > 0)
+      e->max_pairs = n < e->sm_count / 2 ? n : e->sm_count / 2;
+  }
+  cudaGetLastError();
   if (cudaFuncSetAttribute(atc::attn_enc_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::SMEM_BYTES) !=
           cudaSuccess ||
       cudaFuncSetAttribute(atc::attn_enc_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, atc::SMEM_BYTES) !=
@@ -746,7 +759,7 @@ static int gemm_tc_swap_launch(wdz_engine* e, int epi, const GemvMmaParams& g, c
   if (!tc::make_map(&mx, g.x, (uint64_t)g.K, (uint64_t)g.M, 1, (uint64_t)g.ldx * 2, (uint64_t)g.ldx * 2 * g.M,
                     (uint32_t)p.mpad, 2))
     return 1;
-  launch_pdl(e, tc::gemm_tc_swap_kernel, dim3(tiles, ksplit, row_tiles), dim3(tc::THREADS),
+  launch_pdl(e, tc::gemm_tc_swap_kernel, dim3(tiles, ksplit, row_tiles), dim3(tc::SW_THREADS),
              (size_t)tc::sw_smem_bytes(row_tile), s, mw, mx, p);
   WDZ_LAUNCH_CHECK(e, "gemm_tc_swap");
   return WDZ_OK;
@@ -765,6 +778,25 @@ static int gemm_tc_launch(wdz_engine* e, int epi, const GemmParams& p, cudaStrea
   tp.status = e->status;
   const int rpb = p.a_rpb;
   tp.batches = (p.M + rpb - 1) / rpb;
+  // 256-row tiles on CTA pairs wherever a batch has more rows than one CTA's 128
+  const bool pairs = e->max_pairs > 0 && (rpb < p.M ? rpb : p.M) > tc::BM;
+  if (pairs) {
+    tp.tiles_m_per_batch = (rpb + tc2::PAIR_M - 1) / tc2::PAIR_M;
+    tp.tiles_n = p.N / tc2::BN;
+    tp.total_tiles = tp.batches * tp.tiles_m_per_batch * tp.tiles_n;
+    tp.kblocks = p.K / tc::BK;
+    CUtensorMap ma, mw;
+    const uint64_t s1 = (uint64_t)p.lda * 2;
+    const uint64_t s2 = tp.batches > 1 ? (uint64_t)p.a_bstride * 2 : s1 * (uint64_t)rpb;
+    const uint64_t rows_last = tp.batches > 1 ? (uint64_t)rpb : (uint64_t)p.M;
+    if (!tc::make_map(&ma, p.A, (uint64_t)p.K, rows_last, (uint64_t)tp.batches, s1, s2, tc2::BM_CTA, 3)) return 1;
+    if (!tc::make_map(&mw, p.W, (uint64_t)p.K, (uint64_t)p.N, 1, (uint64_t)p.K * 2, (uint64_t)p.K * 2 * p.N, tc2::BN_CTA, 2))
+      return 1;
+    const int n_pairs = tp.total_tiles < e->max_pairs ? tp.total_tiles : e->max_pairs;
+    tc2::gemm_tc2_kernel<<<2 * n_pairs, tc2::THREADS, tc2::SMEM_BYTES, s>>>(ma, mw, tp);
+    WDZ_LAUNCH_CHECK(e, "gemm_tc2");
+    return WDZ_OK;
+  }
   tp.tiles_m_per_batch = (rpb + tc::BM - 1) / tc::BM;
   tp.tiles_n = p.N / tc::BN;
   tp.total_tiles = tp.batches * tp.tiles_m_per_batch * tp.tiles_n;
@@ -1005,9 +1037,12 @@ int wdz_linear(wdz_engine* e, const void* x_dev, int M, int K, const void* w_dev
   cudaStream_t st = (cudaStream_t)s;
   if (e->cfg.dtype == WDZ_F32) return launch_gemm_tile<float, float, float>(e, epi, p, st);
   const int saved = e->cfg.flags;
-  if (cuda_cores_only) e->cfg.flags |= WDZ_FLAG_NO_TENSOR_CORE;
+  const int saved_pairs = e->max_pairs;
+  if (cuda_cores_only == 1) e->cfg.flags |= WDZ_FLAG_NO_TENSOR_CORE;
+  if (cuda_cores_only == 2) e->max_pairs = 0;
   rc = enc_gemm<bf16>(e, epi, p, st);
   e->cfg.flags = saved;
+  e->max_pairs = saved_pairs;
   return rc;
 }
 

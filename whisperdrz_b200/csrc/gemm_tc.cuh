@@ -7,10 +7,13 @@
 //   warp 1      allocates the 512 TMEM columns and issues tcgen05.mma
 //               (M128 N256 K16, four per stage); tcgen05.commit releases the
 //               stage and, after the last k-block, publishes the accumulator
-//   warps 2-5   epilogue: tcgen05.ld of their 32-lane TMEM quadrant, bias /
-//               GELU / residual / positional add / KV-cache scatter, 16-byte
-//               global stores.  Two 256-column accumulators alternate so the
-//               epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 2-9   epilogue: tcgen05.ld of their 32-lane TMEM quadrant (two warps
+//               per quadrant, 128 columns each), bias / GELU / residual /
+//               positional add / KV-cache scatter, 16-byte global stores.  Two
+//               256-column accumulators alternate so the epilogue of tile i
+//               overlaps the main loop of tile i+1.  Eight warps because the
+//               exact-erf GELU is bound by instruction issue: with four, one per
+//               scheduler, the fc1 epilogue took longer than its main loop.
 //
 // The grid is one CTA per SM; tiles are taken round-robin with the N index
 // fastest so that CTAs running together share their A rows through L2.
@@ -31,7 +34,8 @@ namespace tc {
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;                 // two per TMEM lane quadrant, each takes half of a tile's columns
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;  // tiles + barriers + alignment slack
 constexpr long long WAIT_CYCLES = 2000000000ll;                // ~1 s
 
@@ -183,7 +187,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int epi, int
     }
     if (epi == EPI_GELU) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+      for (int i = 0; i < 32; ++i) v[i] = gelu_fast(v[i]);
     }
     uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
@@ -199,23 +203,46 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int epi, int
     float4* d4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + (int64_t)(m / p.c_rpb) * p.c_bstride +
                                            (int64_t)(m % p.c_rpb) * p.ldc + n);
     if (epi == EPI_RESID) {
+      // one addend per element (K is not split here), so a fire-and-forget reduction gives the same fp32 sum as
+      // load-add-store - without the epilogue warps waiting a memory latency per 32 columns
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        float4 t = d4[q];
-        t.x += v[4 * q]; t.y += v[4 * q + 1]; t.z += v[4 * q + 2]; t.w += v[4 * q + 3];
-        d4[q] = t;
-      }
+      for (int q = 0; q < 8; ++q)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                     ::"l"(d4 + q), "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
     } else {  // EPI_GELU_POS
       const float4* pp = reinterpret_cast<const float4*>(p.pos + (int64_t)(m % p.a_rpb) * p.N + n);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         const float4 ps = __ldg(pp + q);
         float4 t;
-        t.x = gelu_erf(v[4 * q]) + ps.x; t.y = gelu_erf(v[4 * q + 1]) + ps.y;
-        t.z = gelu_erf(v[4 * q + 2]) + ps.z; t.w = gelu_erf(v[4 * q + 3]) + ps.w;
+        t.x = gelu_fast(v[4 * q]) + ps.x; t.y = gelu_fast(v[4 * q + 1]) + ps.y;
+        t.z = gelu_fast(v[4 * q + 2]) + ps.z; t.w = gelu_fast(v[4 * q + 3]) + ps.w;
         d4[q] = t;
       }
     }
+  }
+}
+
+// One epilogue warp's share of a tile: NCH chunks of 32 columns from TMEM address taddr, first column n0.  The TMEM
+// load of the next chunk is in flight while the current one goes through bias / activation / stores.
+template <int NCH>
+__device__ __forceinline__ void epilogue_share(const GemmParams& g, int epi, bool row_ok, int m, int n0, uint32_t taddr) {
+  static_assert(NCH % 2 == 0, "chunks are taken in pairs");
+  uint32_t ra[32], rb[32];
+  float v[32];
+  tmem_ld32_raw(taddr, ra);
+#pragma unroll 1
+  for (int c = 0; c < NCH; c += 2) {
+    tmem_wait_ld(ra);
+    tmem_ld32_raw(taddr + (c + 1) * 32, rb);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
+    if (row_ok) epilogue_chunk(g, epi, m, n0 + c * 32, v);
+    tmem_wait_ld(rb);
+    if (c + 2 < NCH) tmem_ld32_raw(taddr + (c + 2) * 32, ra);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rb[i]);
+    if (row_ok) epilogue_chunk(g, epi, m, n0 + (c + 1) * 32, v);
   }
 }
 
@@ -234,7 +261,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(acc_full + i, 1); mbar_init(acc_empty + i, 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(acc_full + i, 1); mbar_init(acc_empty + i, 32 * EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmA) : "memory");
@@ -282,11 +309,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t phase = (it / STAGES) & 1;
           if (!(ok = mbar_wait(full + stage, phase, abort_flag, p.status))) break;
           tc_fence_after();
+          // descriptors once per stage; the next 16 columns of k are 32 bytes on = +2 in the address field (the
+          // issuing thread shares its scheduler with two epilogue warps, every instruction here is paid in MMA gaps)
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
+          const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma(d_tmem, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), (kb | k) != 0);
+            umma(d_tmem, da + (uint64_t)(k * (UMMA_K * 2 >> 4)), db + (uint64_t)(k * (UMMA_K * 2 >> 4)), (kb | k) != 0);
           umma_commit(empty + stage);
         }
         if (ok) umma_commit(acc_full + acc);
@@ -294,6 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else {
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int c0 = ((warp - 2) >> 2) * (BN / 32 / (EPI_WARPS / 4));   // first 32-column chunk of this warp's share
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++local) {
@@ -309,12 +339,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int m = b * p.g.a_rpb + t;
       const bool row_ok = t < p.g.a_rpb && m < p.g.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        float v[32];
-        tmem_ld32(taddr + c * 32, v);
-        if (row_ok) epilogue_chunk(p.g, p.epi, m, nt * BN + c * 32, v);
-      }
+      epilogue_share<BN / 32 / (EPI_WARPS / 4)>(p.g, p.epi, row_ok, m, nt * BN + c0 * 32, taddr + c0 * 32);
       tc_fence_before();
       mbar_arrive(acc_empty + acc);
     }
@@ -341,6 +366,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // Epilogue thread = one feature (TMEM lane), columns = rows.
 // ---------------------------------------------------------------------------
 constexpr int SW_STAGES = 4;
+constexpr int SW_THREADS = 192;   // producer warp, MMA warp, four epilogue warps
 constexpr int SW_STAGE_BYTES = A_BYTES + 256 * BK * 2;   // W tile + up to 256 rows of x
 constexpr int SW_SMEM_BYTES = SW_STAGES * SW_STAGE_BYTES + 256 + 1024;   // largest launch
 inline int sw_smem_bytes(int row_tile) { return SW_STAGES * (A_BYTES + row_tile * BK * 2) + 256 + 1024; }
@@ -367,7 +393,7 @@ __device__ __forceinline__ void umma_idesc(uint32_t d_tmem, uint64_t da, uint64_
       ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(SW_THREADS, 1)
 gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const TcSwapParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -426,10 +452,10 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (!(ok = mbar_wait(full + stage, phase, abort_flag, p.status))) break;
         tc_fence_after();
         const uint32_t w_addr = smem_u32(smem + stage * stage_bytes);
-        const uint32_t x_addr = w_addr + w_bytes;
+        const uint64_t dw = umma_desc(w_addr), dx = umma_desc(w_addr + w_bytes);
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_idesc(tmem_base, umma_desc(w_addr + k * UMMA_K * 2), umma_desc(x_addr + k * UMMA_K * 2), p.idesc, (i | k) != 0);
+          umma_idesc(tmem_base, dw + (uint64_t)(k * (UMMA_K * 2 >> 4)), dx + (uint64_t)(k * (UMMA_K * 2 >> 4)), p.idesc, (i | k) != 0);
         umma_commit(empty + stage);
       }
       if (ok) umma_commit(acc_full);
@@ -468,7 +494,7 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
           bf16* dst = reinterpret_cast<bf16*>(p.y) + (int64_t)c * p.ldy + n;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (j < rows) dst[(int64_t)j * p.ldy] = from_f<bf16>(gelu_erf(__uint_as_float(r[j]) + bias));
+            if (j < rows) dst[(int64_t)j * p.ldy] = from_f<bf16>(gelu_fast(__uint_as_float(r[j]) + bias));
         } else if (p.epi == EPI_SW_QKV_CACHE && n >= p.d) {
           const bool is_v = n >= 2 * p.d;
           bf16* cache = is_v ? p.cache_v : p.cache_k;

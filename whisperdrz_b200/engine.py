@@ -279,8 +279,9 @@ class Engine:
         return xa
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gelu: bool = False,
-               cuda_cores_only: bool = False) -> torch.Tensor:
-        """act(x @ w.T + bias) in the engine dtype through the engine's GEMM kernels."""
+               cuda_cores_only: bool | int = False) -> torch.Tensor:
+        """act(x @ w.T + bias) in the engine dtype through the engine's GEMM kernels (``cuda_cores_only``: True/1 =
+        no tensor cores, 2 = the lone-CTA tcgen05 kernel, no CTA pairs)."""
         x = x.to(device=self.device, dtype=self.dtype).contiguous()
         w = w.to(device=self.device, dtype=self.dtype).contiguous()
         b = None if bias is None else bias.to(device=self.device, dtype=self.dtype).contiguous()
