@@ -200,7 +200,7 @@ def align(dims, sd, n_chunks=8, n_ids=440, reps=3):
     return out
 
 
-def products(dims, sd, row_counts=(32, 256), once=False):
+def products(dims, sd, row_counts=(32, 256, 384), once=False):
     """``once``: every shape launched a single time outside a graph, on cold weights (for profiler captures)."""
     small = ModelDimensions.from_name("test-small")
     e = Engine(small, init_state_dict(small, 0), dtype=torch.bfloat16, n_slots=2, max_clips=1)

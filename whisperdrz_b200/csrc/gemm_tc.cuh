@@ -363,10 +363,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // (about 0.3-0.4 us per 64-wide k-block), not by the weight stream.  With
 // more than one K split the partial sums are added to the fp32 output with
 // red.global.add (residual-stream epilogue only).
-// Epilogue thread = one feature (TMEM lane), columns = rows.
+// Epilogue thread = one feature (TMEM lane), columns = rows; eight epilogue
+// warps, two per lane quadrant, each taking half of the row tile.
 // ---------------------------------------------------------------------------
 constexpr int SW_STAGES = 4;
-constexpr int SW_THREADS = 192;   // producer warp, MMA warp, four epilogue warps
+constexpr int SW_THREADS = 320;   // producer warp, MMA warp, eight epilogue warps (two per TMEM lane quadrant)
 constexpr int SW_STAGE_BYTES = A_BYTES + 256 * BK * 2;   // W tile + up to 256 rows of x
 constexpr int SW_SMEM_BYTES = SW_STAGES * SW_STAGE_BYTES + 256 + 1024;   // largest launch
 inline int sw_smem_bytes(int row_tile) { return SW_STAGES * (A_BYTES + row_tile * BK * 2) + 256 + 1024; }
@@ -478,18 +479,11 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         const int rows = min(32, p.M - c);
         if (p.epi == EPI_RESID) {
           float* dst = reinterpret_cast<float*>(p.y) + (int64_t)c * p.ldy + n;
-          if (gridDim.y > 1) {
+          // fire-and-forget adds, also without a K split (one addend per element then: the same fp32 sum as
+          // load-add-store, without the loads' latency)
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < rows) atomicAdd(dst + (int64_t)j * p.ldy, __uint_as_float(r[j]) + bias);
-          } else {
-            float old[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) old[j] = j < rows ? dst[(int64_t)j * p.ldy] : 0.0f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < rows) dst[(int64_t)j * p.ldy] = old[j] + __uint_as_float(r[j]) + bias;
-          }
+          for (int j = 0; j < 32; ++j)
+            if (j < rows) atomicAdd(dst + (int64_t)j * p.ldy, __uint_as_float(r[j]) + bias);
         } else if (p.epi == EPI_GELU) {
           bf16* dst = reinterpret_cast<bf16*>(p.y) + (int64_t)c * p.ldy + n;
 #pragma unroll
@@ -515,15 +509,19 @@ gemm_tc_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             if (j < rows) dst[(int64_t)j * p.ldy] = __uint_as_float(r[j]) + bias;
         }
       };
+      // the two warps of a lane quadrant split the row tile's 32-row groups: the epilogue runs after the main loop
+      // (one tile per CTA), so its length is paid in full on every product
+      const int groups = p.mpad >> 5, mid = (groups + 1) >> 1;
+      const int c_lo = ((warp - 2) >> 2) ? mid * 32 : 0, c_hi = ((warp - 2) >> 2) ? groups * 32 : mid * 32;
       uint32_t ra[32], rb[32];
-      tmem_ld32_raw(taddr, ra);
-      for (int c = 0; c < p.mpad; c += 64) {
+      if (c_lo < c_hi) tmem_ld32_raw(taddr + c_lo, ra);
+      for (int c = c_lo; c < c_hi; c += 64) {
         tmem_wait_ld(ra);
-        if (c + 32 < p.mpad) tmem_ld32_raw(taddr + c + 32, rb);
+        if (c + 32 < c_hi) tmem_ld32_raw(taddr + c + 32, rb);
         if (row0 + c < p.M) emit(row0 + c, ra);
-        if (c + 32 < p.mpad) {
+        if (c + 32 < c_hi) {
           tmem_wait_ld(rb);
-          if (c + 64 < p.mpad) tmem_ld32_raw(taddr + c + 64, ra);
+          if (c + 64 < c_hi) tmem_ld32_raw(taddr + c + 64, ra);
           if (row0 + c + 32 < p.M) emit(row0 + c + 32, rb);
         }
       }
