@@ -128,3 +128,32 @@ def test_engine_refuses_to_run_without_cuda():
     dims = ModelDimensions.from_name("test-tiny")
     with pytest.raises(RuntimeError):
         Engine(dims, {}, dtype=torch.float32)
+
+
+def test_gelu_fast_polynomial_as_written_in_the_kernel_source():
+    """The branch-free GELU of the bf16 tensor-core epilogues (``csrc/common.cuh: gelu_fast``): the coefficients are
+    read out of the CUDA source, the formula is restated in float32 numpy, and the result is held against
+    0.5 x (1 + erf(x / sqrt 2)) in float64 over the whole range - the bound the header comment and the design state."""
+    from scipy.special import erf
+    src = open(os.path.join(ROOT, "whisperdrz_b200", "csrc", "common.cuh")).read()
+    body = src[src.index("float gelu_fast(float x)"):]
+    body = body[:body.index("\n}\n")]
+    first = re.search(r"float q = (-?[0-9.e+-]+)f;", body).group(1)
+    rest = re.findall(r"q = fmaf\(q, a, (-?[0-9.e+-]+)f\);", body)
+    coef = [np.float32(first)] + [np.float32(c) for c in rest]
+    assert len(coef) == 7 and "fminf(fabsf(z), 4.0f)" in body
+    f = np.float32
+    x = np.linspace(-12.0, 12.0, 1_200_001).astype(f)
+    z = (x * f(0.70710678118654752440)).astype(f)
+    a = np.minimum(np.abs(z), f(4.0))
+    q = np.full_like(a, coef[0])
+    for c in coef[1:]:
+        q = (q * a + c).astype(f)
+    e = np.exp2((-q * a).astype(f)).astype(f)
+    er = np.copysign((f(1.0) - e).astype(f), z)
+    h = (f(0.5) * x).astype(f)
+    got = (h * er + h).astype(f).astype(np.float64)
+    xd = x.astype(np.float64)
+    ref = 0.5 * xd * (1.0 + erf(xd / np.sqrt(2.0)))
+    assert np.abs(er.astype(np.float64) - erf(z.astype(np.float64))).max() < 2.5e-7      # erf itself, exact 2^x
+    assert np.abs(got - ref).max() < 1e-6                                                  # the GELU value
