@@ -55,6 +55,7 @@ typedef struct wdz_config {
 #define WDZ_FLAG_NO_TENSOR_CORE 1 /* keep bf16 GEMMs on the CUDA-core path (debug / A-B runs) */
 #define WDZ_FLAG_NO_GRAPH 4       /* launch the decode step kernel by kernel instead of replaying a CUDA graph */
 #define WDZ_FLAG_NO_PDL 8         /* decode kernels launched without programmatic dependent launch */
+#define WDZ_FLAG_NO_SPLIT_STEP 32 /* decode steps of many rows as one batch on one stream (no half-batch overlap) */
 #define WDZ_FLAG_NO_CTA_PAIRS 16  /* encoder-shaped GEMMs on lone CTAs (128x256 tiles) instead of CTA pairs (256x256) */
 #define WDZ_FLAG_NO_BULK_COPY 2   /* cross-attention through plain loads instead of the bulk-copy ring */
 

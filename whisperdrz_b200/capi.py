@@ -17,6 +17,7 @@ FLAG_NO_BULK_COPY = 2
 FLAG_NO_GRAPH = 4
 FLAG_NO_PDL = 8
 FLAG_NO_CTA_PAIRS = 16
+FLAG_NO_SPLIT_STEP = 32
 MODE_OR, MODE_ALL_EXCEPT_TABLE, MODE_ALL_EXCEPT_RANGE, MODE_ALL = 0, 1, 2, 3
 MAX_TABLES = 32
 PROF_KINDS = {"cross_attn": 0, "self_attn": 1, "dec_gemm": 2, "enc_gemm": 3, "enc_attn": 4, "lm_head": 5,

@@ -111,6 +111,12 @@ struct wdz_engine {
   TsParams ts_params{50257, 50365, 51865, 50, 100, 1u, 2u};
   static constexpr int gemv_max_rows = 16;   // up to this many rows the mma.sync weight-streaming kernel runs, above it tcgen05
   cudaStream_t cap_stream = nullptr;  // capture happens here (the caller's stream may be the legacy default stream)
+  // A decode step of many rows runs its layers as two half-batches on two streams (forked and joined with events, also
+  // under capture), so that one half's products fill the SMs and the time in which the other half's attention streams
+  // the K/V caches; created with the workspace, never during a capture.
+  cudaStream_t side_stream = nullptr;
+  bool pdl_suppress = false;   // the next launches go out without programmatic dependent launch
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_phase = nullptr;
 
   // optional per-kernel timing (wdz_profile): event pairs around selected launches
   struct Span { cudaEvent_t a, b; int kind; double work; };
@@ -154,6 +160,7 @@ namespace {
 
 size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
 constexpr int SW_MAX_ROWS = 512;   // token rows per launch of the operand-swapped decode product
+constexpr int SPLIT_MIN_ROWS = 320;  // a decode step of at least this many rows runs as two half-batches on two streams
 
 // Launch with the programmatic stream-serialization attribute (kernels that call pdl_wait()).
 template <typename... KArgs, typename... Args>
@@ -165,7 +172,7 @@ void launch_pdl(wdz_engine* e, void (*kern)(KArgs...), dim3 grid, dim3 block, si
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = (e->cfg.flags & WDZ_FLAG_NO_PDL) ? 0 : 1;
+  cfg.numAttrs = ((e->cfg.flags & WDZ_FLAG_NO_PDL) || e->pdl_suppress) ? 0 : 1;
   cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
@@ -387,25 +394,30 @@ int cross_kv_impl(wdz_engine* e, const void* xa, const int* slot_ids, int B, cud
 
 // ---- decoder ---------------------------------------------------------------
 template <typename T>
-int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool cross, cudaStream_t s) {
+int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool cross, cudaStream_t s, int sm_cap = 0,
+                    int64_t part_cap = 0) {
   const int H = e->cfg.n_text_head;
   const bool stream = e->stream_attn_ok;
+  // sm_cap > 0: a half-batch of a split step - walk the items with at most sm_cap CTAs and leave the other SMs to the
+  // other half's products; part_cap: this half's share of the partial-result buffers
+  const int sms = sm_cap > 0 && stream ? sm_cap : e->sm_count;
+  const int64_t part_entries = part_cap > 0 ? part_cap : e->part_entries;
   int splits;
   // The streaming kernel walks (key range, row) items.  With few rows one persistent CTA per SM takes several items
   // and keeps its ring running across them (a 32-row step has only a wave or two of items, and every fresh CTA pays
   // the ring's start); with many rows one CTA per item does better, because a finished CTA's successor starts on
   // the hardware's own schedule while an item change inside a CTA stalls its head warps on the next query.
-  const bool persistent = stream && rows < 128;
+  const bool persistent = stream && (rows < 128 || sm_cap > 0);
   if (stream && !cross) {
     // lengths are only known on the device: fixed ranges, items past a row's length are skipped
-    p.chunk = persistent ? 64 : 128;
+    p.chunk = rows < 128 ? 64 : 128;
   } else if (stream) {
     // pick the split count whose items fill the SMs most evenly (whole waves of CTAs, or equal shares per CTA)
     int best = 1;
     double best_util = 0.0;
-    for (int c = 1; c <= (rows <= 4 ? 46 : 24) && (int64_t)rows * c <= e->part_entries && max_len / c >= 32; ++c) {
-      const int items = rows * c, per_cta = (items + e->sm_count - 1) / e->sm_count;
-      const double util = (double)items / ((double)per_cta * e->sm_count);
+    for (int c = 1; c <= (rows <= 4 ? 46 : 24) && (int64_t)rows * c <= part_entries && max_len / c >= 32; ++c) {
+      const int items = rows * c, per_cta = (items + sms - 1) / sms;
+      const double util = (double)items / ((double)per_cta * sms);
       if (util > best_util + 0.03) { best_util = util; best = c; }
     }
     p.chunk = (max_len + best - 1) / best;
@@ -418,17 +430,17 @@ int attn_dec_launch(wdz_engine* e, AttnDecParams p, int rows, int max_len, bool 
     p.chunk = 64;
   }
   splits = (max_len + p.chunk - 1) / p.chunk;
-  if ((int64_t)rows * splits > e->part_entries)
+  if ((int64_t)rows * splits > part_entries)
     return e->fail(WDZ_ECAPACITY, "attention partials: %d rows x %d splits exceed the workspace", rows, splits);
   p.max_splits = splits;
   const int sp = e->span_begin(cross ? WDZ_PROF_CROSS_ATTN : WDZ_PROF_SELF_ATTN,
                                cross ? 2.0 * rows * max_len * p.d * sizeof(T) : 0.0, s);
   if (stream) {
-    p.counters = e->att_counters;   // the last item of a row merges the row: no combine launch
+    if (!p.counters) p.counters = e->att_counters;   // the last item of a row merges the row: no combine launch
     p.rows = rows;
     p.split_major = persistent ? 1 : 0;
     const int items = splits * rows;
-    launch_pdl(e, attn_dec_stream_kernel<T>, dim3(persistent && items > e->sm_count ? e->sm_count : items), dim3((H + 1) * 32),
+    launch_pdl(e, attn_dec_stream_kernel<T>, dim3(persistent && items > sms ? sms : items), dim3((H + 1) * 32),
                attn_dec_stream_smem<T>(p.d), s, p, e->status);
     e->span_end(sp, s);
     WDZ_LAUNCH_CHECK(e, "attn_dec_stream");
@@ -504,82 +516,165 @@ int forward_rows_impl(wdz_engine* e, const int* tokens, const int* slots, const 
   launch_pdl(e, embed_kernel<T>, dim3(n), dim3(256), 0, s, tokens, positions, (const T*)e->tok_emb, (const T*)e->dec_pos, e->dx, n, d,
                                      c.n_vocab, c.n_text_ctx);
   WDZ_LAUNCH_CHECK(e, "embed");
-  AttnDecParams ap{};
-  ap.n_slots = c.n_slots; ap.d = d; ap.slots = slots;
-  ap.part_o = e->part_o; ap.part_ml = e->part_ml; ap.out = ao; ap.ldo = d;
-  // y = epi(x W^T + b) with x in T; RESID accumulates into the fp32 residual stream
-  // next_w / next_bytes: the weights the following product will stream; the small-row kernel (<= 16 rows) pulls a
-  // share of them into L2 while it runs, the many-row tcgen05 kernel ignores them
-  auto gemm = [&](int epi, const T* x, int64_t ldx, const void* W, const void* bias, void* y, int64_t ldy, int M,
-                  int N, int K, const void* next_w = nullptr, size_t next_bytes = 0) -> int {
-    if constexpr (kBf16) {
-      GemvMmaParams p = mma_params(x, ldx, W, bias, y, ldy, M, N, K);
-      p.next_w = next_w; p.next_bytes = next_bytes;
-      switch (epi) {
-        case EPI_STORE: return launch_gemv_mma<EPI_STORE, false>(e, p, s);
-        case EPI_RESID: return launch_gemv_mma<EPI_RESID, false>(e, p, s);
-        case EPI_GELU: return launch_gemv_mma<EPI_GELU, true>(e, p, s);
-        default: return e->fail(WDZ_EINVAL, "bad decode epilogue %d", epi);
+  // The layers over rows [r0, r0 + m) on stream st.  sm_cap / part_off / part_cap: see attn_dec_launch - a half-batch
+  // of a split step walks its attention items with sm_cap CTAs and owns half of the partial-result buffers.
+  auto run_layers = [&](int r0, int m, cudaStream_t st, int sm_cap, int64_t part_off, int64_t part_cap,
+                        cudaEvent_t record_before_first_cross) -> int {
+    const int* sl = slots + r0;
+    const int* ps = positions + r0;
+    float* dx = e->dx + (int64_t)r0 * d;
+    T* xn_ = xn + (int64_t)r0 * d;
+    T* ao_ = ao + (int64_t)r0 * d;
+    T* hid_ = hid + (int64_t)r0 * 4 * d;
+    float* dqkv = e->dqkv + (int64_t)r0 * 3 * d;
+    float* dq = e->dq + (int64_t)r0 * d;
+    const int H = c.n_text_head;
+    AttnDecParams ap{};
+    ap.n_slots = c.n_slots; ap.d = d; ap.slots = sl;
+    ap.part_o = e->part_o + part_off * H * HD; ap.part_ml = e->part_ml + part_off * H * 2; ap.out = ao_; ap.ldo = d;
+    ap.counters = e->att_counters + r0;
+    // y = epi(x W^T + b) with x in T; RESID accumulates into the fp32 residual stream
+    // next_w / next_bytes: the weights the following product will stream; the small-row kernel (<= 16 rows) pulls a
+    // share of them into L2 while it runs, the many-row tcgen05 kernel ignores them
+    auto gemm = [&](int epi, const T* x, int64_t ldx, const void* W, const void* bias, void* y, int64_t ldy, int M,
+                    int N, int K, const void* next_w = nullptr, size_t next_bytes = 0) -> int {
+      if constexpr (kBf16) {
+        GemvMmaParams p = mma_params(x, ldx, W, bias, y, ldy, M, N, K);
+        p.next_w = next_w; p.next_bytes = next_bytes;
+        switch (epi) {
+          case EPI_STORE: return launch_gemv_mma<EPI_STORE, false>(e, p, st);
+          case EPI_RESID: return launch_gemv_mma<EPI_RESID, false>(e, p, st);
+          case EPI_GELU: return launch_gemv_mma<EPI_GELU, true>(e, p, st);
+          default: return e->fail(WDZ_EINVAL, "bad decode epilogue %d", epi);
+        }
+      } else {
+        return dec_gemm<T>(e, epi, (const float*)x, ldx, W, bias, (float*)y, ldy, M, N, K, nullptr, st);
       }
-    } else {
-      return dec_gemm<T>(e, epi, (const float*)x, ldx, W, bias, (float*)y, ldy, M, N, K, nullptr, s);
+    };
+    int rc;
+    // In a split step the product that follows an attention kernel goes out WITHOUT programmatic dependent launch:
+    // launched early, its CTAs would sit on the SMs the attention walk leaves free, waiting for that attention to
+    // end - exactly the SMs the other half's products are meant to run on (measured: 6033 ms per benchmark step with
+    // the early launch, 5510 without).
+    const bool plain_after_attention = part_cap > 0;
+    for (int l = 0; l < c.n_text_layer; ++l) {
+      const LayerW& w = e->dec[l];
+      const size_t wb = (size_t)d * d * sizeof(T);   // bytes of one d x d weight
+      const void* after = l + 1 < c.n_text_layer ? e->dec[l + 1].qkv_w : e->tok_emb;
+      const size_t after_bytes = l + 1 < c.n_text_layer ? 3 * wb : (size_t)32 << 20;   // a first slice of the LM head
+      if ((rc = launch_ln<T, T>(e, dx, d, nullptr, w.ln1_w, w.ln1_b, xn_, d, m, d, st))) return rc;
+      if constexpr (kBf16) {
+        // fused QKV projection whose epilogue appends K and V to the slot cache
+        GemvMmaParams p = mma_params(xn_, d, w.qkv_w, w.qkv_b, dqkv, 3 * d, m, 3 * d, d);
+        p.cache_k = (bf16*)e->self_k; p.cache_v = (bf16*)e->self_v; p.slots = sl; p.positions = ps;
+        p.layer = l; p.n_slots = c.n_slots; p.S = c.max_tokens; p.d = d;
+        p.next_w = w.out_w; p.next_bytes = wb;
+        if ((rc = launch_gemv_mma<EPI_QKV_CACHE, false>(e, p, st))) return rc;
+      } else {
+        if ((rc = gemm(EPI_STORE, xn_, d, w.qkv_w, w.qkv_b, dqkv, 3 * d, m, 3 * d, d))) return rc;
+        launch_pdl(e, kv_append_kernel<T>, dim3(m), dim3(256), 0, st, dqkv, sl, ps, (T*)e->self_k, (T*)e->self_v, l, c.n_slots,
+                                               c.max_tokens, d, m);
+        WDZ_LAUNCH_CHECK(e, "kv_append");
+      }
+      ap.layer = l;
+      ap.q = dqkv; ap.ldq = 3 * d; ap.cache_k = e->self_k; ap.cache_v = e->self_v; ap.S = c.max_tokens;
+      ap.positions = ps; ap.fixed_len = 0;
+      if ((rc = attn_dec_launch<T>(e, ap, m, c.max_tokens, false, st, sm_cap, part_cap))) return rc;
+      e->pdl_suppress = plain_after_attention;
+      rc = gemm(EPI_RESID, ao_, d, w.out_w, w.out_b, dx, d, m, d, d, w.xq_w, wb);
+      e->pdl_suppress = false;
+      if (rc) return rc;
+
+      // The cross-attention query is a complete-sum product of only d features: as such it would stream its
+      // weights through a tenth of the SMs.  Its LayerNorm clears the query buffer instead and the product runs as
+      // K-split partial sums added into it, like the residual products.
+      const bool split_q = kBf16 && m > e->gemv_max_rows && m <= 1024 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE);
+      if ((rc = launch_ln<T, T>(e, dx, d, nullptr, w.lnx_w, w.lnx_b, xn_, d, m, d, st, split_q ? dq : nullptr, d, d))) return rc;
+      if ((rc = gemm(split_q ? EPI_RESID : EPI_STORE, xn_, d, w.xq_w, w.xq_b, dq, d, m, d, d, w.xout_w, wb))) return rc;
+      if (cap) {
+        int here = 0;
+        for (int j = 0; j < e->al_heads.n; ++j) here += e->al_heads.layer[j] == l;
+        if (here > 0) {
+          align_capture_kernel<float><<<m, 64 * here, 0, st>>>(dq, d, m, l, e->al_heads, cap->qcap, cap->rows_total, cap->row_base);
+          e->launches += 1;
+          WDZ_LAUNCH_CHECK(e, "align_capture");
+        }
+        if (l >= e->al_last_layer) return 1;   // later layers cannot change the captured queries
+      }
+      if (l == 0) {
+        // the two halves of a split step start half a layer apart, so that one is in its products while the other
+        // streams its cross K/V
+        if (record_before_first_cross && cudaEventRecord(record_before_first_cross, st) != cudaSuccess) {
+          cudaError_t ce = cudaGetLastError();
+          return e->fail(WDZ_ECUDA, "event record: %s", cudaGetErrorString(ce));
+        }
+      }
+      ap.q = dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
+      ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
+      if ((rc = attn_dec_launch<T>(e, ap, m, c.n_audio_ctx, true, st, sm_cap, part_cap))) return rc;
+      e->pdl_suppress = plain_after_attention;
+      rc = gemm(EPI_RESID, ao_, d, w.xout_w, w.xout_b, dx, d, m, d, d, w.fc1_w, 4 * wb);
+      e->pdl_suppress = false;
+      if (rc) return rc;
+
+      if ((rc = launch_ln<T, T>(e, dx, d, nullptr, w.ln2_w, w.ln2_b, xn_, d, m, d, st))) return rc;
+      if ((rc = gemm(EPI_GELU, xn_, d, w.fc1_w, w.fc1_b, hid_, 4 * d, m, 4 * d, d, w.fc2_w, 4 * wb))) return rc;
+      if ((rc = gemm(EPI_RESID, hid_, 4 * d, w.fc2_w, w.fc2_b, dx, d, m, d, 4 * d, after, after_bytes))) return rc;
     }
+    return WDZ_OK;
   };
-  for (int l = 0; l < c.n_text_layer; ++l) {
-    const LayerW& w = e->dec[l];
-    const size_t wb = (size_t)d * d * sizeof(T);   // bytes of one d x d weight
-    const void* after = l + 1 < c.n_text_layer ? e->dec[l + 1].qkv_w : e->tok_emb;
-    const size_t after_bytes = l + 1 < c.n_text_layer ? 3 * wb : (size_t)32 << 20;   // a first slice of the LM head
-    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln1_w, w.ln1_b, xn, d, n, d, s))) return rc;
-    if constexpr (kBf16) {
-      // fused QKV projection whose epilogue appends K and V to the slot cache
-      GemvMmaParams p = mma_params(xn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d);
-      p.cache_k = (bf16*)e->self_k; p.cache_v = (bf16*)e->self_v; p.slots = slots; p.positions = positions;
-      p.layer = l; p.n_slots = c.n_slots; p.S = c.max_tokens; p.d = d;
-      p.next_w = w.out_w; p.next_bytes = wb;
-      if ((rc = launch_gemv_mma<EPI_QKV_CACHE, false>(e, p, s))) return rc;
-    } else {
-      if ((rc = gemm(EPI_STORE, xn, d, w.qkv_w, w.qkv_b, e->dqkv, 3 * d, n, 3 * d, d))) return rc;
-      launch_pdl(e, kv_append_kernel<T>, dim3(n), dim3(256), 0, s, e->dqkv, slots, positions, (T*)e->self_k, (T*)e->self_v, l, c.n_slots,
-                                             c.max_tokens, d, n);
-      WDZ_LAUNCH_CHECK(e, "kv_append");
-    }
-    ap.layer = l;
-    ap.q = e->dqkv; ap.ldq = 3 * d; ap.cache_k = e->self_k; ap.cache_v = e->self_v; ap.S = c.max_tokens;
-    ap.positions = positions; ap.fixed_len = 0;
-    if ((rc = attn_dec_launch<T>(e, ap, n, c.max_tokens, false, s))) return rc;
-    if ((rc = gemm(EPI_RESID, ao, d, w.out_w, w.out_b, e->dx, d, n, d, d, w.xq_w, wb))) return rc;
 
-    // The cross-attention query is a complete-sum product of only d features: as such it would stream its
-    // weights through a tenth of the SMs.  Its LayerNorm clears the query buffer instead and the product runs as
-    // K-split partial sums added into it, like the residual products.
-    const bool split_q = kBf16 && n > e->gemv_max_rows && n <= 1024 && !(c.flags & WDZ_FLAG_NO_TENSOR_CORE);
-    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.lnx_w, w.lnx_b, xn, d, n, d, s, split_q ? e->dq : nullptr, d, d))) return rc;
-    if ((rc = gemm(split_q ? EPI_RESID : EPI_STORE, xn, d, w.xq_w, w.xq_b, e->dq, d, n, d, d, w.xout_w, wb))) return rc;
-    if (cap) {
-      int here = 0;
-      for (int j = 0; j < e->al_heads.n; ++j) here += e->al_heads.layer[j] == l;
-      if (here > 0) {
-        align_capture_kernel<float><<<n, 64 * here, 0, s>>>(e->dq, d, n, l, e->al_heads, cap->qcap, cap->rows_total, cap->row_base);
-        e->launches += 1;
-        WDZ_LAUNCH_CHECK(e, "align_capture");
-      }
-      if (l >= e->al_last_layer) return WDZ_OK;   // later layers cannot change the captured queries
+  // Many rows: two half-batches on two streams.  The decode step alternates between products (tensor cores, weights)
+  // and attention (HBM, almost no arithmetic); with the halves half a layer apart one half's attention streams its
+  // K/V while the other half's products run on the SMs the attention walk leaves free.
+  const bool split = kBf16 && !cap && !e->profiling && e->side_stream && e->stream_attn_ok && n >= SPLIT_MIN_ROWS &&
+                     !(c.flags & (WDZ_FLAG_NO_SPLIT_STEP | WDZ_FLAG_NO_TENSOR_CORE));
+  if (!split) {
+    rc = run_layers(0, n, s, 0, 0, 0, nullptr);
+    if (rc == 1) return WDZ_OK;   // alignment capture complete
+    if (rc) return rc;
+  } else {
+    const int na = ((n + 1) / 2 + 31) / 32 * 32, nb = n - na;   // n >= SPLIT_MIN_ROWS, so both halves have rows
+    const int64_t half = e->part_entries / 2;
+    // CTAs of a half's attention walk: about two thirds of the SMs (the rest stay free for the other half's products),
+    // trimmed so that every CTA gets the same number of whole rows - 96 CTAs of two rows each for a 192-row half,
+    // where 92 or 105 CTAs measured 5 % slower per benchmark step
+    const int sm_share = e->sm_count - e->sm_count / 3;
+    auto attn_ctas_for = [&](int m) {
+      const int per_cta = (m + sm_share - 1) / sm_share;
+      const int ctas = (m + per_cta - 1) / per_cta;
+      return ctas >= sm_share - sm_share / 5 ? ctas : sm_share;
+    };
+    cudaStream_t s2 = e->side_stream;
+    bool ok = cudaEventRecord(e->ev_fork, s) == cudaSuccess && cudaStreamWaitEvent(s2, e->ev_fork, 0) == cudaSuccess;
+    if (ok) {
+      // the second half waits until the first has reached its first cross-attention
+      rc = run_layers(0, na, s, attn_ctas_for(na), 0, half, e->ev_phase);
+      if (rc) return rc;
+      ok = cudaStreamWaitEvent(s2, e->ev_phase, 0) == cudaSuccess;
     }
-    ap.q = e->dq; ap.ldq = d; ap.cache_k = e->cross_k; ap.cache_v = e->cross_v; ap.S = c.n_audio_ctx;
-    ap.positions = nullptr; ap.fixed_len = c.n_audio_ctx;
-    if ((rc = attn_dec_launch<T>(e, ap, n, c.n_audio_ctx, true, s))) return rc;
-    if ((rc = gemm(EPI_RESID, ao, d, w.xout_w, w.xout_b, e->dx, d, n, d, d, w.fc1_w, 4 * wb))) return rc;
-
-    if ((rc = launch_ln<T, T>(e, e->dx, d, nullptr, w.ln2_w, w.ln2_b, xn, d, n, d, s))) return rc;
-    if ((rc = gemm(EPI_GELU, xn, d, w.fc1_w, w.fc1_b, hid, 4 * d, n, 4 * d, d, w.fc2_w, 4 * wb))) return rc;
-    if ((rc = gemm(EPI_RESID, hid, 4 * d, w.fc2_w, w.fc2_b, e->dx, d, n, d, 4 * d, after, after_bytes))) return rc;
+    if (ok) {
+      rc = run_layers(na, nb, s2, attn_ctas_for(nb), half, half, nullptr);
+      if (rc) return rc;
+      ok = cudaEventRecord(e->ev_join, s2) == cudaSuccess && cudaStreamWaitEvent(s, e->ev_join, 0) == cudaSuccess;
+    }
+    if (!ok) {
+      cudaError_t ce = cudaGetLastError();
+      return e->fail(WDZ_ECUDA, "split step fork/join: %s", cudaGetErrorString(ce));
+    }
   }
   launch_pdl(e, bump_seqlens_kernel, dim3((n + 255) / 256), dim3(256), 0, s, slots, positions, e->seq_lens, n, c.n_slots);
   WDZ_LAUNCH_CHECK(e, "bump_seqlens");
   // final LayerNorm on the emit rows only, then the tied LM head (model.py:609-613)
   if ((rc = launch_ln<T, T>(e, e->dx, d, emit_rows, e->dec_ln_w, e->dec_ln_b, xn, d, n_emit, d, s))) return rc;
-  if ((rc = gemm(EPI_STORE, xn, d, e->tok_emb, nullptr, e->logits, c.n_vocab, n_emit, c.n_vocab, d))) return rc;
+  if constexpr (kBf16) {
+    GemvMmaParams p = mma_params(xn, d, e->tok_emb, nullptr, e->logits, c.n_vocab, n_emit, c.n_vocab, d);
+    if ((rc = launch_gemv_mma<EPI_STORE, false>(e, p, s))) return rc;
+  } else {
+    if ((rc = dec_gemm<T>(e, EPI_STORE, (const float*)xn, d, e->tok_emb, nullptr, e->logits, c.n_vocab, n_emit, c.n_vocab,
+                          d, nullptr, s)))
+      return rc;
+  }
   e->last_emit = n_emit;
   return WDZ_OK;
 }
@@ -853,6 +948,10 @@ int wdz_engine_destroy(wdz_engine* e) {
     for (auto& g : e->step_graphs) cudaGraphExecDestroy(g.second.exec);
     for (auto& g : e->ts_graphs) cudaGraphExecDestroy(g.second.exec);
     if (e->cap_stream) cudaStreamDestroy(e->cap_stream);
+    if (e->side_stream) cudaStreamDestroy(e->side_stream);
+    if (e->ev_fork) cudaEventDestroy(e->ev_fork);
+    if (e->ev_join) cudaEventDestroy(e->ev_join);
+    if (e->ev_phase) cudaEventDestroy(e->ev_phase);
   }
   delete e;
   return WDZ_OK;
@@ -882,6 +981,17 @@ int wdz_set_workspace(wdz_engine* e, void* dev, size_t bytes) {
       cudaMemset(e->att_counters, 0, sizeof(int) * e->cfg.max_rows) != cudaSuccess) {
     cudaGetLastError();
     return e->fail(WDZ_ECUDA, "cannot clear the status word");
+  }
+  // second stream and events of the split decode step (host objects, no device memory); without them the step
+  // simply runs as one batch
+  if (!e->side_stream && e->cfg.max_rows >= SPLIT_MIN_ROWS && !(e->cfg.flags & WDZ_FLAG_NO_SPLIT_STEP)) {
+    if (cudaStreamCreateWithFlags(&e->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&e->ev_phase, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      if (e->side_stream) { cudaStreamDestroy(e->side_stream); e->side_stream = nullptr; }
+    }
   }
   return WDZ_OK;
 }
