@@ -306,7 +306,8 @@ def main():
     h2d = args.clips * 480000 * 4 + rule_bytes + 8 * n_tok_e // max(args.steps, 1)
     d2h = 4 * n_tok_e // max(args.steps, 1)
 
-    # roofline of the dominant kernel, from one extra profiled step
+    # roofline of the dominant kernel, from one extra profiled step (kernel by kernel outside the graph, the whole batch
+    # on one stream: the timed steps overlap two half-batches, where a launch's duration is not the kernel's alone)
     eng.profile(True)
     one_step(audio_dev)
     prof = eng.profile_read()
