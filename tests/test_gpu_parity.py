@@ -290,6 +290,42 @@ def test_tensor_core_gelu_epilogue_against_exact_erf(small_bf16):
         assert (got[big] != ref.float().bfloat16().double()[big]).double().mean() < 0.005
 
 
+def test_split_decode_step_matches_the_unsplit_step():
+    """A step of 352 rows runs as two half-batches on two streams; with ``FLAG_NO_SPLIT_STEP`` it runs as one batch.
+    Same kernels on the same operands, only the K-split partial sums arrive in another order: the logits agree within
+    bf16 order noise (2e-2 x RMS, the bound used between the two product kernels below), over a prompt pass and two
+    single-token steps, and the split engine launches about twice as many kernels per step."""
+    from whisperdrz_b200 import capi
+    n = 352
+    e, dims, sd = _engine("test-small", torch.bfloat16, n_slots=n, max_clips=4, max_rows=2 * n)
+    e2, _, _ = _engine("test-small", torch.bfloat16, n_slots=n, max_clips=4, max_rows=2 * n, flags=capi.FLAG_NO_SPLIT_STEP)
+    rng = np.random.default_rng(5)
+    audio = torch.from_numpy(synth.clips([41, 42, 43, 44])).cuda()
+    slots = list(range(n))
+    first = [int(t) for t in rng.integers(0, 50000, n)]
+    out, counts = [], []
+    for eng in (e, e2):
+        xa = eng.encode(eng.logmel(audio))
+        for i in range(0, n, 4):
+            eng.cross_kv(xa, slots[i: i + 4])
+        eng.slot_reset(slots)
+        steps = []
+        tok = first
+        for pos in range(3):
+            before = eng.launch_count()
+            lg = eng.forward_rows(tok, slots, [pos] * n, emit_rows=list(range(n)))
+            counts.append(eng.launch_count() - before)
+            steps.append(lg.float().cpu())
+            tok = [int(t) for t in steps[-1].argmax(-1)] if eng is e else [int(t) for t in out[0][pos].argmax(-1)]
+        eng.device_status()
+        out.append(steps)
+    for a, b in zip(out[0], out[1]):
+        rms = b.pow(2).mean().sqrt()
+        assert (a - b).abs().max() < 2e-2 * rms
+    assert counts[0] > 1.8 * counts[3]          # split: every layer kernel once per half
+    e.close(); e2.close()
+
+
 def test_decoder_bf16_many_rows_tensor_core_path():
     """More than 16 token rows per call take the operand-swapped tcgen05 product
     (prefill of ~150 prompt rows, then decode steps over 20 slots at different
